@@ -1,0 +1,151 @@
+// Shared device helpers: packed loads/stores of 2..8 channels, fast/precise transcendental
+// variants, host-side argument checks.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hawk_b200.h"
+
+namespace hawk {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kGateC = -8.0f;  // hawk/scan_fused.py:44,123
+
+// ---- argument checks (host) ---------------------------------------------------------------
+#define HAWK_REQUIRE(cond, code) \
+  do {                           \
+    if (!(cond)) return (code);  \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline bool valid_dtype(int d) { return d == HAWK_F32 || d == HAWK_BF16; }
+inline size_t dtype_size(int d) { return d == HAWK_BF16 ? 2 : 4; }
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? HAWK_OK : HAWK_ERR_LAUNCH; }
+
+// ---- two adjacent channels ----------------------------------------------------------------
+// bf16 -> fp32 is a 16-bit shift, so a packed pair unpacks with one shift and one mask.
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename T>
+struct Pair;  // raw storage of two adjacent channels
+template <>
+struct Pair<float> {
+  using raw = float2;
+  static __device__ __forceinline__ raw zero() { return make_float2(0.f, 0.f); }
+  static __device__ __forceinline__ raw load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+  static __device__ __forceinline__ float2 unpack(raw r) { return r; }
+  static __device__ __forceinline__ void store(float* p, float lo, float hi) {
+    *reinterpret_cast<float2*>(p) = make_float2(lo, hi);
+  }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  using raw = uint32_t;
+  static __device__ __forceinline__ raw zero() { return 0u; }
+  static __device__ __forceinline__ raw load(const __nv_bfloat16* p) {
+    return __ldg(reinterpret_cast<const uint32_t*>(p));
+  }
+  static __device__ __forceinline__ float2 unpack(raw r) { return unpack_bf16x2(r); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float lo, float hi) {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(lo, hi);
+  }
+};
+
+// ---- VEC adjacent channels (VEC = 4 or 8) as fp32 registers --------------------------------
+template <typename T, int VEC>
+struct VecIO;
+template <int VEC>
+struct VecIO<float, VEC> {
+  static_assert(VEC % 4 == 0, "VEC must be a multiple of 4");
+  static __device__ __forceinline__ void load(const float* p, float (&v)[VEC]) {
+#pragma unroll
+    for (int q = 0; q < VEC / 4; ++q) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p) + q);
+      v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+    }
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[VEC]) {
+#pragma unroll
+    for (int q = 0; q < VEC / 4; ++q)
+      reinterpret_cast<float4*>(p)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  }
+};
+template <>
+struct VecIO<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(p));
+    const float2 a = unpack_bf16x2(r.x), b = unpack_bf16x2(r.y), c = unpack_bf16x2(r.z), d = unpack_bf16x2(r.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 r;
+    r.x = pack_bf16x2(v[0], v[1]);
+    r.y = pack_bf16x2(v[2], v[3]);
+    r.z = pack_bf16x2(v[4], v[5]);
+    r.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+};
+template <>
+struct VecIO<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(p));
+    const float2 a = unpack_bf16x2(r.x), b = unpack_bf16x2(r.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 r;
+    r.x = pack_bf16x2(v[0], v[1]);
+    r.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
+// ---- transcendental variants ---------------------------------------------------------------
+// FAST = one MUFU instruction each (bf16 storage hides their ~1e-7 error);
+// precise = the CUDA math library's fp32 functions (for fp32 storage, 1e-5 parity).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_f(float g) {
+  if (FAST) {
+    // clamp keeps 1 + 2^(..) finite; sigmoid(+-30) is 1 / 9e-14 already
+    float e = ex2_approx(-kLog2e * fminf(fmaxf(g, -30.f), 30.f));
+    return rcp_approx(1.f + e);
+  } else {
+    return 1.f / (1.f + expf(-g));
+  }
+}
+
+__device__ __forceinline__ float softplus_f(float v) { return log1pf(expf(v)); }  // scan_fused.py:18-20
+
+}  // namespace hawk

@@ -1,0 +1,332 @@
+// Width-W (W <= 4) causal depthwise temporal convolution, forward and backward, one pass each.
+//
+// Replaces the eager loop of hawk/external.py:49-95 (W shifted multiply-adds over zero-padded
+// copies, ~13 tensor passes) and its autograd backward.  HBM-bound: every thread owns VEC
+// adjacent channels (one 16-byte load per row) and walks a tile of consecutive time steps with the
+// last W-1 rows held in registers, so each input row is read once (plus a W-1 row halo per tile).
+// The input may be a strided view (the x half of the [B,T,2R] projection, hawk/hawk.py:164-166).
+//
+//   y[b,t,d]  = bias[d] + sum_k w[W-1-k,d] x[b,t-k,d]                       (external.py:78-93)
+//   dx[b,t,d] = sum_k w[W-1-k,d] go[b,t+k,d]
+//   dw[W-1-k,d] = sum_{b,t} go[b,t,d] x[b,t-k,d],   dbias[d] = sum_{b,t} go[b,t,d]
+// Parameter gradients: per-thread fp32 partials -> shared-memory sum over the CTA's time tiles
+// -> one partial row per CTA in the workspace -> fixed-order final reduction (deterministic).
+#include "common.cuh"
+
+namespace hawk {
+
+constexpr int kConvFwdVec = 8;
+constexpr int kConvFwdRows = 32;  // time steps per thread
+constexpr int kConvBwdVec = 4;
+constexpr int kConvBwdRows = 32;
+constexpr int kConvBwdTilesPerCta = 8;
+
+template <typename TI, typename TO, int W>
+__global__ void __launch_bounds__(256)
+conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const float* __restrict__ w,
+                  const float* __restrict__ bias, TO* __restrict__ y, int B, int T, int D, int n_ttiles) {
+  constexpr int VEC = kConvFwdVec, TR = kConvFwdRows;
+  const int nvec = D / VEC;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cv = (int)(gid % nvec);
+  const int tt = (int)((gid / nvec) % n_ttiles);
+  const int64_t b = gid / ((int64_t)nvec * n_ttiles);
+  if (b >= B) return;
+  const int d0 = cv * VEC;
+  const int t0 = tt * TR;
+  const TI* xp = x + b * xbs + d0;
+  TO* yp = y + ((int64_t)b * T) * D + d0;
+
+  float wv[W][VEC], bv[VEC];
+#pragma unroll
+  for (int j = 0; j < W; ++j) VecIO<float, VEC>::load(w + (int64_t)j * D + d0, wv[j]);
+  VecIO<float, VEC>::load(bias + d0, bv);
+
+  // win[j] = x[t-1-j]; rows before the sequence start are zero (external.py:123-136)
+  float win[W > 1 ? W - 1 : 1][VEC];
+#pragma unroll
+  for (int j = 0; j < W - 1; ++j) {
+    const int t = t0 - 1 - j;
+    if (t >= 0) {
+      VecIO<TI, VEC>::load(xp + (int64_t)t * xrs, win[j]);
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) win[j][v] = 0.f;
+    }
+  }
+
+  constexpr int U = 4;  // rows loaded together
+  for (int tb = 0; tb < TR; tb += U) {
+    float cur[U][VEC];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + tb + u;
+      if (t < T) VecIO<TI, VEC>::load(xp + (int64_t)t * xrs, cur[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + tb + u;
+      if (t >= T) break;
+      float out[VEC];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        float acc = wv[W - 1][v] * cur[u][v];
+#pragma unroll
+        for (int k = 1; k < W; ++k) acc = fmaf(wv[W - 1 - k][v], win[k - 1][v], acc);
+        out[v] = acc + bv[v];
+      }
+      VecIO<TO, VEC>::store(yp + (int64_t)t * D, out);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+#pragma unroll
+        for (int j = W - 2; j > 0; --j) win[j][v] = win[j - 1][v];
+        if (W > 1) win[0][v] = cur[u][v];
+      }
+    }
+  }
+}
+
+template <typename TG, typename TX, int W>
+__global__ void __launch_bounds__(256)
+conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t xbs, int64_t xrs,
+                  const float* __restrict__ w, TX* __restrict__ dx, int64_t dxbs, int64_t dxrs,
+                  float* __restrict__ partial, int T, int D, int n_ttiles) {
+  constexpr int VEC = kConvBwdVec, TR = kConvBwdRows, TY = kConvBwdTilesPerCta;
+  constexpr int NACC = W + 1;  // W weight rows + bias
+  __shared__ float red[TY][NACC * VEC][32];
+
+  const int lane = threadIdx.x & 31;
+  const int ty = threadIdx.x >> 5;
+  const int nvec = D / VEC;
+  const int cv = blockIdx.x * 32 + lane;
+  const int tt = blockIdx.y * TY + ty;
+  const int b = blockIdx.z;
+  const bool active = cv < nvec && tt < n_ttiles;
+
+  float acc[NACC][VEC];
+#pragma unroll
+  for (int j = 0; j < NACC; ++j)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[j][v] = 0.f;
+
+  if (active) {
+    const int d0 = cv * VEC;
+    const int t0 = tt * TR;
+    const TX* xp = x + (int64_t)b * xbs + d0;
+    const TG* gp = go + ((int64_t)b * T) * D + d0;
+    TX* dxp = dx + (int64_t)b * dxbs + d0;
+
+    float wv[W][VEC];
+#pragma unroll
+    for (int j = 0; j < W; ++j) VecIO<float, VEC>::load(w + (int64_t)j * D + d0, wv[j]);
+
+    // xw[j] = x[t-j] (j = 1..W-1 held, j = 0 loaded per step); gw[j] = go[t+j] (j = 0..W-1)
+    float xw[W][VEC], gw[W][VEC];
+#pragma unroll
+    for (int j = 1; j < W; ++j) {
+      const int t = t0 - j;
+      if (t >= 0) {
+        VecIO<TX, VEC>::load(xp + (int64_t)t * xrs, xw[j]);
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) xw[j][v] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) {  // go[t0 .. t0+W-2]; go[t+W-1] arrives inside the loop
+      const int t = t0 + j;
+      if (t < T) {
+        VecIO<TG, VEC>::load(gp + (int64_t)t * D, gw[j]);
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) gw[j][v] = 0.f;
+      }
+    }
+
+    constexpr int U = 4;
+    for (int tb = 0; tb < TR; tb += U) {
+      float xin[U][VEC], gin[U][VEC];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int t = t0 + tb + u;
+        if (t < T) VecIO<TX, VEC>::load(xp + (int64_t)t * xrs, xin[u]);
+        if (t + W - 1 < T) {
+          VecIO<TG, VEC>::load(gp + (int64_t)(t + W - 1) * D, gin[u]);
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) gin[u][v] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int t = t0 + tb + u;
+        if (t >= T) break;
+        float out[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          xw[0][v] = xin[u][v];
+          gw[W - 1][v] = gin[u][v];
+          float s = 0.f;
+#pragma unroll
+          for (int k = 0; k < W; ++k) {
+            s = fmaf(wv[W - 1 - k][v], gw[k][v], s);                          // dx
+            acc[W - 1 - k][v] = fmaf(gw[0][v], xw[k][v], acc[W - 1 - k][v]);  // dw
+          }
+          acc[W][v] += gw[0][v];  // dbias
+          out[v] = s;
+        }
+        VecIO<TX, VEC>::store(dxp + (int64_t)t * dxrs, out);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+#pragma unroll
+          for (int j = W - 1; j > 0; --j) xw[j][v] = xw[j - 1][v];
+#pragma unroll
+          for (int j = 0; j < W - 1; ++j) gw[j][v] = gw[j + 1][v];
+        }
+      }
+    }
+  }
+
+  // sum the CTA's TY time tiles, then one partial row per CTA
+#pragma unroll
+  for (int j = 0; j < NACC; ++j)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) red[ty][j * VEC + v][lane] = acc[j][v];
+  __syncthreads();
+  if (cv < nvec) {
+    const int64_t row = (int64_t)blockIdx.z * gridDim.y + blockIdx.y;
+    for (int q = ty; q < NACC * VEC; q += TY) {
+      float s = 0.f;
+#pragma unroll
+      for (int y2 = 0; y2 < TY; ++y2) s += red[y2][q][lane];
+      const int j = q / VEC, v = q % VEC;
+      partial[(row * NACC + j) * D + cv * VEC + v] = s;
+    }
+  }
+}
+
+// out[j][d] = sum_rows partial[row][j][d];  j < W -> dw, j == W -> dbias
+__global__ void conv1d_param_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                           float* __restrict__ dbias, int64_t nrows, int D, int W) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)(W + 1) * D) return;
+  const int j = (int)(idx / D), d = (int)(idx % D);
+  float s = 0.f;
+  for (int64_t r = 0; r < nrows; ++r) s += partial[(r * (W + 1) + j) * D + d];
+  if (j < W) dw[(int64_t)j * D + d] = s; else dbias[d] = s;
+}
+
+static int64_t conv_bwd_rows(int B, int T) {
+  const int n_ttiles = (T + kConvBwdRows - 1) / kConvBwdRows;
+  return (int64_t)B * ((n_ttiles + kConvBwdTilesPerCta - 1) / kConvBwdTilesPerCta);
+}
+
+template <typename TI, typename TO>
+static int conv_fwd_dispatch(const void* x, int64_t xbs, int64_t xrs, const float* w, const float* bias, void* y,
+                             int B, int T, int D, int W, cudaStream_t st) {
+  const int n_ttiles = (T + kConvFwdRows - 1) / kConvFwdRows;
+  const int64_t threads = (int64_t)B * n_ttiles * (D / kConvFwdVec);
+  const int64_t blocks = (threads + 255) / 256;
+  HAWK_REQUIRE(blocks <= 0x7fffffffLL, HAWK_ERR_SHAPE);
+#define HAWK_CONV_FWD(WW)                                                                                \
+  conv1d_fwd_kernel<TI, TO, WW><<<(unsigned)blocks, 256, 0, st>>>(static_cast<const TI*>(x), xbs, xrs, w, bias, \
+                                                                  static_cast<TO*>(y), B, T, D, n_ttiles)
+  switch (W) {
+    case 1: HAWK_CONV_FWD(1); break;
+    case 2: HAWK_CONV_FWD(2); break;
+    case 3: HAWK_CONV_FWD(3); break;
+    case 4: HAWK_CONV_FWD(4); break;
+    default: return HAWK_ERR_UNSUPPORTED;
+  }
+#undef HAWK_CONV_FWD
+  return launch_status();
+}
+
+template <typename TG, typename TX>
+static int conv_bwd_dispatch(const void* go, const void* x, int64_t xbs, int64_t xrs, const float* w, void* dx,
+                             int64_t dxbs, int64_t dxrs, float* dw, float* dbias, float* partial, int B, int T,
+                             int D, int W, cudaStream_t st) {
+  const int n_ttiles = (T + kConvBwdRows - 1) / kConvBwdRows;
+  const int nvec = D / kConvBwdVec;
+  dim3 grid((nvec + 31) / 32, (n_ttiles + kConvBwdTilesPerCta - 1) / kConvBwdTilesPerCta, B);
+  HAWK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, HAWK_ERR_SHAPE);
+#define HAWK_CONV_BWD(WW)                                                                                   \
+  conv1d_bwd_kernel<TG, TX, WW><<<grid, 256, 0, st>>>(static_cast<const TG*>(go), static_cast<const TX*>(x), xbs, xrs, \
+                                                      w, static_cast<TX*>(dx), dxbs, dxrs, partial, T, D, n_ttiles)
+  switch (W) {
+    case 1: HAWK_CONV_BWD(1); break;
+    case 2: HAWK_CONV_BWD(2); break;
+    case 3: HAWK_CONV_BWD(3); break;
+    case 4: HAWK_CONV_BWD(4); break;
+    default: return HAWK_ERR_UNSUPPORTED;
+  }
+#undef HAWK_CONV_BWD
+  int rc = launch_status();
+  if (rc != HAWK_OK) return rc;
+  const int64_t n = (int64_t)(W + 1) * D;
+  conv1d_param_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partial, dw, dbias, conv_bwd_rows(B, T), D, W);
+  return launch_status();
+}
+
+static int check_conv(int B, int T, int D, int W) {
+  HAWK_REQUIRE(B >= 1 && T >= 1 && D >= 8 && D % 8 == 0, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(W >= 1 && W <= 4, HAWK_ERR_UNSUPPORTED);
+  return HAWK_OK;
+}
+
+}  // namespace hawk
+
+using namespace hawk;
+
+extern "C" int hawk_conv1d_fwd(const void* x, int64_t x_batch_stride, int64_t x_row_stride, const float* w,
+                               const float* bias, void* y, int B, int T, int D, int W, int in_dtype,
+                               int out_dtype, void* stream) {
+  HAWK_REQUIRE(x && w && bias && y, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(in_dtype) && valid_dtype(out_dtype), HAWK_ERR_DTYPE);
+  int rc = check_conv(B, T, D, W);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(x_row_stride >= D && x_batch_stride >= 0, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(y, 16) && aligned(w, 16) && aligned(bias, 16) && x_row_stride % 8 == 0 &&
+                   x_batch_stride % 8 == 0,
+               HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  using bf = __nv_bfloat16;
+  if (in_dtype == HAWK_BF16 && out_dtype == HAWK_BF16)
+    return conv_fwd_dispatch<bf, bf>(x, x_batch_stride, x_row_stride, w, bias, y, B, T, D, W, st);
+  if (in_dtype == HAWK_BF16 && out_dtype == HAWK_F32)
+    return conv_fwd_dispatch<bf, float>(x, x_batch_stride, x_row_stride, w, bias, y, B, T, D, W, st);
+  if (in_dtype == HAWK_F32 && out_dtype == HAWK_F32)
+    return conv_fwd_dispatch<float, float>(x, x_batch_stride, x_row_stride, w, bias, y, B, T, D, W, st);
+  return conv_fwd_dispatch<float, bf>(x, x_batch_stride, x_row_stride, w, bias, y, B, T, D, W, st);
+}
+
+extern "C" size_t hawk_conv1d_bwd_workspace_bytes(int B, int T, int D, int W) {
+  if (B < 1 || T < 1 || D < 1 || W < 1) return 0;
+  return (size_t)conv_bwd_rows(B, T) * (size_t)(W + 1) * (size_t)D * sizeof(float);
+}
+
+extern "C" int hawk_conv1d_bwd(const void* go, const void* x, int64_t x_batch_stride, int64_t x_row_stride,
+                               const float* w, void* dx, int64_t dx_batch_stride, int64_t dx_row_stride,
+                               float* dw, float* dbias, void* workspace, size_t workspace_bytes, int B, int T,
+                               int D, int W, int go_dtype, int x_dtype, void* stream) {
+  HAWK_REQUIRE(go && x && w && dx && dw && dbias, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(go_dtype) && valid_dtype(x_dtype), HAWK_ERR_DTYPE);
+  int rc = check_conv(B, T, D, W);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(x_row_stride >= D && dx_row_stride >= D && x_batch_stride >= 0 && dx_batch_stride >= 0, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(workspace && workspace_bytes >= hawk_conv1d_bwd_workspace_bytes(B, T, D, W), HAWK_ERR_WORKSPACE);
+  HAWK_REQUIRE(aligned(go, 16) && aligned(x, 16) && aligned(dx, 16) && aligned(w, 16) && aligned(workspace, 16) &&
+                   x_row_stride % 8 == 0 && x_batch_stride % 8 == 0 && dx_row_stride % 8 == 0 &&
+                   dx_batch_stride % 8 == 0,
+               HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  using bf = __nv_bfloat16;
+  if (go_dtype == HAWK_BF16 && x_dtype == HAWK_BF16)
+    return conv_bwd_dispatch<bf, bf>(go, x, x_batch_stride, x_row_stride, w, dx, dx_batch_stride, dx_row_stride, dw, dbias, partial, B, T, D, W, st);
+  if (go_dtype == HAWK_F32 && x_dtype == HAWK_BF16)
+    return conv_bwd_dispatch<float, bf>(go, x, x_batch_stride, x_row_stride, w, dx, dx_batch_stride, dx_row_stride, dw, dbias, partial, B, T, D, W, st);
+  if (go_dtype == HAWK_F32 && x_dtype == HAWK_F32)
+    return conv_bwd_dispatch<float, float>(go, x, x_batch_stride, x_row_stride, w, dx, dx_batch_stride, dx_row_stride, dw, dbias, partial, B, T, D, W, st);
+  return conv_bwd_dispatch<bf, float>(go, x, x_batch_stride, x_row_stride, w, dx, dx_batch_stride, dx_row_stride, dw, dbias, partial, B, T, D, W, st);
+}

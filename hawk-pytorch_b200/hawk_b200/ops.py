@@ -1,0 +1,300 @@
+"""The reference's three hot-path operators, backed by the sm_100a kernels.
+
+Same names and call signatures as the reference so that hawk/hawk.py can bind them in
+place of its own (hawk/hawk.py:12-14):
+
+    fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param) -> h        hawk/scan_fused.py:445
+    Conv1D(width, temporal_width, w_init_variance_scale)(x) -> y   hawk/external.py:12-98
+    fused_cross_entropy(lm_head_weight, act, labels) -> loss       hawk/fused_cross_entropy.py:77-79
+
+plus the two halves of the cached decode step (hawk/hawk.py:137-151,168-199).
+
+Each op is a torch.library custom op (with a fake/meta kernel and a registered backward), so
+torch.compile treats it as an opaque call; the real implementation hands raw device pointers
+and the current CUDA stream to the C ABI in libhawk_b200.so.  There is no CPU path: tensors
+must live on a CUDA device and the library must have been built.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DT = {torch.float32: _lib.HAWK_F32, torch.bfloat16: _lib.HAWK_BF16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"hawk_b200: unsupported dtype {t.dtype} (float32 and bfloat16 only)") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("hawk_b200: tensors must be on a CUDA device (there is no CPU path)")
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class _on:
+    """Makes the tensor's device current for the duration of a launch (no-op when it already is)."""
+
+    def __init__(self, t):
+        if not t.is_cuda:
+            raise RuntimeError("hawk_b200: tensors must be on a CUDA device (there is no CPU path)")
+        self.idx = t.device.index
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and self.idx != cur:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *a):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
+# ---------------------------------------------------------------------------------------------
+# RG-LRU scan
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("hawk_b200::scan_fwd", mutates_args=())
+def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
+             h0: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _lib.load()
+    B, T, D = x.shape
+    x, gx, ga, lam = x.contiguous(), gx.contiguous(), ga.contiguous(), lam.contiguous()
+    if h0 is not None:
+        h0 = h0.contiguous()
+    h = torch.empty_like(x)
+    with _on(x):
+        _lib.check(lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
+                                     h.data_ptr(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd")
+    return h
+
+
+@scan_fwd.register_fake
+def _(x, gx, ga, lam, h0=None):
+    return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("hawk_b200::scan_bwd", mutates_args=())
+def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor, h0: Optional[torch.Tensor],
+             h: torch.Tensor, go: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    B, T, D = x.shape
+    x, gx, ga, lam, h, go = (t.contiguous() for t in (x, gx, ga, lam, h, go))
+    if go.dtype != x.dtype:
+        go = go.to(x.dtype)
+    dx, dgx, dga = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    dlam = torch.empty(D, dtype=torch.float32, device=x.device)
+    dh0 = torch.empty(B, D, dtype=torch.float32, device=x.device)
+    ws_bytes = lib.hawk_scan_bwd_workspace_bytes(B, D)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    if h0 is not None:
+        h0 = h0.contiguous()
+    with _on(x):
+        _lib.check(lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
+                                     h.data_ptr(), go.data_ptr(), dx.data_ptr(), dgx.data_ptr(), dga.data_ptr(),
+                                     dlam.data_ptr(), dh0.data_ptr(), ws.data_ptr(), ws_bytes, B, T, D, _dt(x),
+                                     _stream(x)), "hawk_scan_bwd")
+    return dx, dgx, dga, dlam, dh0
+
+
+@scan_bwd.register_fake
+def _(x, gx, ga, lam, h0, h, go):
+    B, T, D = x.shape
+    e = lambda: torch.empty_like(x, memory_format=torch.contiguous_format)
+    return e(), e(), e(), x.new_empty(D, dtype=torch.float32), x.new_empty(B, D, dtype=torch.float32)
+
+
+def _scan_setup(ctx, inputs, output):
+    x, gx, ga, lam, h0 = inputs
+    ctx.save_for_backward(x, gx, ga, lam, h0, output)
+    ctx.has_h0 = h0 is not None
+
+
+def _scan_backward(ctx, go):
+    x, gx, ga, lam, h0, h = ctx.saved_tensors
+    dx, dgx, dga, dlam, dh0 = scan_bwd(x, gx, ga, lam, h0, h, go)
+    return dx, dgx, dga, dlam, (dh0 if ctx.has_h0 else None)
+
+
+scan_fwd.register_autograd(_scan_backward, setup_context=_scan_setup)
+
+
+def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None):
+    """h = RG-LRU scan of (x, input-gate pre-activation, recurrence-gate pre-activation, Lambda).
+
+    Drop-in for hawk/scan_fused.py:445.  As in the reference (custom_fwd(cast_inputs=bfloat16),
+    scan_fused.py:428) the three activation tensors are taken in bf16 under CUDA autocast and in
+    their own dtype otherwise, and h has that dtype.  Lambda and its gradient stay fp32 here (the
+    reference rounds Lambda to bf16 under autocast).  `h0` ([B,D], optional) is an extension;
+    the default reproduces the reference's zero initial state.
+    """
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.bfloat16
+    else:
+        dt = x.dtype
+    x, x_rg_lru, a_rg_lru = (t if t.dtype == dt else t.to(dt) for t in (x, x_rg_lru, a_rg_lru))
+    lam = a_param if a_param.dtype == torch.float32 else a_param.float()
+    if h0 is not None and h0.dtype != torch.float32:
+        h0 = h0.float()
+    return scan_fwd(x, x_rg_lru, a_rg_lru, lam, h0)
+
+
+# ---------------------------------------------------------------------------------------------
+# temporal conv1d
+# ---------------------------------------------------------------------------------------------
+def _conv_view(x: torch.Tensor) -> torch.Tensor:
+    """x as the kernels can read it in place: [B,T,D], unit channel stride, 16-byte aligned rows."""
+    ok = (x.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+          and x.stride(1) >= x.shape[2])
+    return x if ok else x.contiguous()
+
+
+@torch.library.custom_op("hawk_b200::conv1d_fwd", mutates_args=())
+def conv1d_fwd(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    lib = _lib.load()
+    B, T, D = x.shape
+    xv = _conv_view(x)
+    w, b = w.contiguous(), b.contiguous()
+    y = torch.empty(B, T, D, dtype=out_dtype, device=x.device)
+    with _on(x):
+        _lib.check(lib.hawk_conv1d_fwd(xv.data_ptr(), xv.stride(0), xv.stride(1), w.data_ptr(), b.data_ptr(),
+                                       y.data_ptr(), B, T, D, w.shape[0], _dt(xv), _DT[out_dtype], _stream(x)),
+                   "hawk_conv1d_fwd")
+    return y
+
+
+@conv1d_fwd.register_fake
+def _(x, w, b, out_dtype):
+    return x.new_empty(x.shape, dtype=out_dtype)
+
+
+@torch.library.custom_op("hawk_b200::conv1d_bwd", mutates_args=())
+def conv1d_bwd(go: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    B, T, D = x.shape
+    W = w.shape[0]
+    xv = _conv_view(x)
+    go, w = go.contiguous(), w.contiguous()
+    dx = torch.empty(B, T, D, dtype=x.dtype, device=x.device)
+    dw = torch.empty(W, D, dtype=torch.float32, device=x.device)
+    db = torch.empty(D, dtype=torch.float32, device=x.device)
+    ws_bytes = lib.hawk_conv1d_bwd_workspace_bytes(B, T, D, W)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with _on(x):
+        _lib.check(lib.hawk_conv1d_bwd(go.data_ptr(), xv.data_ptr(), xv.stride(0), xv.stride(1), w.data_ptr(),
+                                       dx.data_ptr(), dx.stride(0), dx.stride(1), dw.data_ptr(), db.data_ptr(),
+                                       ws.data_ptr(), ws_bytes, B, T, D, W, _dt(go), _dt(xv), _stream(x)),
+                   "hawk_conv1d_bwd")
+    return dx, dw, db
+
+
+@conv1d_bwd.register_fake
+def _(go, x, w):
+    return (x.new_empty(x.shape), w.new_empty(w.shape, dtype=torch.float32),
+            w.new_empty(w.shape[1], dtype=torch.float32))
+
+
+def _conv_setup(ctx, inputs, output):
+    x, w, b, _ = inputs
+    ctx.save_for_backward(x, w)
+    ctx.w_dtype, ctx.b_dtype = w.dtype, b.dtype
+
+
+def _conv_backward(ctx, go):
+    x, w = ctx.saved_tensors
+    dx, dw, db = conv1d_bwd(go, x, w)
+    return dx, dw, db, None
+
+
+conv1d_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
+
+
+def temporal_conv1d(x, w, b, *, out_dtype=None):
+    """y[b,t,d] = bias[d] + sum_k w[W-1-k,d] x[b,t-k,d] (zero history).  x may be a strided view.
+
+    out_dtype=None gives the reference's result type (promotion of x and w dtypes: fp32 for a
+    bf16 x under autocast, hawk/external.py:88-93); pass x.dtype to have the kernel round on
+    store instead of running a separate cast.
+    """
+    if out_dtype is None:
+        out_dtype = torch.promote_types(x.dtype, w.dtype)
+    w32 = w if w.dtype == torch.float32 else w.float()
+    b32 = b if b.dtype == torch.float32 else b.float()
+    return conv1d_fwd(x, w32, b32, out_dtype)
+
+
+class Conv1D(nn.Module):
+    """Drop-in for hawk/external.py:12-150: same constructor, parameter names (`w` [temporal_width,
+    width], `b` [width], fp32) and initialisation (external.py:40-47)."""
+
+    def __init__(self, width: int, temporal_width: int, w_init_variance_scale: float = 0.01):
+        super().__init__()
+        self.width = width
+        self.temporal_width = temporal_width
+        self.w_init_variance_scale = w_init_variance_scale
+        self.w = nn.Parameter(torch.empty([temporal_width, width], dtype=torch.float32))
+        self.b = nn.Parameter(torch.empty([width], dtype=torch.float32))
+        self.out_dtype = None  # None = reference promotion; set to e.g. torch.bfloat16 to fuse the cast
+        nn.init.normal_(self.w, mean=0.0, std=math.sqrt(w_init_variance_scale / temporal_width))
+        nn.init.zeros_(self.b)
+
+    def forward(self, x):
+        return temporal_conv1d(x, self.w, self.b, out_dtype=self.out_dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# cached decode step
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("hawk_b200::decode_conv_step", mutates_args=("conv_state",))
+def decode_conv_step(x_new: torch.Tensor, conv_state: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """x_new [B,D] (row-strided ok), conv_state [B,W-1,D] contiguous, rolled in place. Returns y [B,D]."""
+    lib = _lib.load()
+    B, D = x_new.shape
+    if x_new.stride(1) != 1 or x_new.stride(0) % 8 or x_new.data_ptr() % 16:
+        x_new = x_new.contiguous()
+    assert conv_state.is_contiguous() and conv_state.shape == (B, w.shape[0] - 1, D)
+    y = torch.empty(B, D, dtype=x_new.dtype, device=x_new.device)
+    with _on(x_new):
+        _lib.check(lib.hawk_decode_conv_step(x_new.data_ptr(), x_new.stride(0), conv_state.data_ptr(), w.data_ptr(),
+                                             b.data_ptr(), y.data_ptr(), B, D, w.shape[0], _dt(x_new),
+                                             _dt(conv_state), _stream(x_new)), "hawk_decode_conv_step")
+    return y
+
+
+@decode_conv_step.register_fake
+def _(x_new, conv_state, w, b):
+    return x_new.new_empty(x_new.shape)
+
+
+@torch.library.custom_op("hawk_b200::decode_rglru_step", mutates_args=("state",))
+def decode_rglru_step(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
+                      state: torch.Tensor) -> torch.Tensor:
+    """One recurrence step on [B,D]; `state` is overwritten with h; returns h in x's dtype."""
+    lib = _lib.load()
+    B, D = x.shape
+    x, gx, ga = x.contiguous(), gx.contiguous(), ga.contiguous()
+    assert state.is_contiguous() and state.shape == (B, D)
+    h = torch.empty_like(x)
+    with _on(x):
+        _lib.check(lib.hawk_decode_rglru_step(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(),
+                                              state.data_ptr(), h.data_ptr(), B, D, _dt(x), _dt(state), _stream(x)),
+                   "hawk_decode_rglru_step")
+    return h
+
+
+@decode_rglru_step.register_fake
+def _(x, gx, ga, lam, state):
+    return torch.empty_like(x)

@@ -1,0 +1,116 @@
+/*
+ * hawk_b200 -- C ABI of the B200 (sm_100a) kernels for Hawk's data-parallel hot path.
+ *
+ * The reference (fattorib/hawk-pytorch) has no FFI: its seam is three Python names
+ * imported into hawk/hawk.py:12-14 (Conv1D, fused_cross_entropy, fused_linear_scan) plus
+ * the eager decode step in Hawk.forward.  Each entry point below names the reference code
+ * it stands in for.  The Python side of the boundary (hawk_b200.ops) binds these with
+ * ctypes and keeps the reference's call signatures.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless said otherwise;
+ *   - nothing here allocates, frees or synchronises: outputs and scratch ("workspace") are
+ *     passed in by the caller, sized by the *_workspace_bytes helpers;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns;
+ *   - return value: HAWK_OK (0) or a negative hawk_status; hawk_strerror() gives the text;
+ *     arguments are validated on the host before anything is launched;
+ *   - tensors are row-major with the channel (last) dimension contiguous.  `dtype` selects the
+ *     storage type of activations (HAWK_F32 or HAWK_BF16); arithmetic is always fp32;
+ *     Lambda, conv weights/bias and all parameter gradients are fp32.
+ */
+#ifndef HAWK_B200_H_
+#define HAWK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HAWK_B200_ABI_VERSION 1
+
+typedef enum hawk_dtype { HAWK_F32 = 0, HAWK_BF16 = 1 } hawk_dtype;
+
+typedef enum hawk_status {
+  HAWK_OK = 0,
+  HAWK_ERR_NULL = -1,        /* a required pointer is NULL */
+  HAWK_ERR_SHAPE = -2,       /* a dimension is out of range or not a supported multiple */
+  HAWK_ERR_DTYPE = -3,       /* unknown dtype enum */
+  HAWK_ERR_ALIGN = -4,       /* a pointer or stride breaks the stated alignment */
+  HAWK_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  HAWK_ERR_LAUNCH = -6,      /* the CUDA runtime refused a launch (cudaGetLastError) */
+  HAWK_ERR_UNSUPPORTED = -7, /* valid request this build does not implement */
+  HAWK_ERR_DEVICE = -8       /* wrong device / driver entry point unavailable */
+} hawk_status;
+
+/* ABI version of the loaded library (HAWK_B200_ABI_VERSION at build time). */
+int hawk_version(void);
+/* Static, NUL-terminated description of a hawk_status. */
+const char* hawk_strerror(int status);
+
+/* ------------------------------------------------------------------------------------------
+ * RG-LRU scan.  Replaces hawk/scan_fused.py:319-360 (sequential_scan_forward + the Triton
+ * kernel :34-109) and :363-424 (sequential_scan_backward + kernel :112-317, including the
+ * batch sum of the Lambda gradient at :424).
+ *
+ *   i = sigmoid(gx), r = sigmoid(ga), a = exp(-8 r softplus(lam)),
+ *   h_t = a_t h_{t-1} + x_t i_t sqrt(1 - a_t^2),   h_{-1} = h0 (zero when h0 == NULL).
+ *
+ * x, gx, ga, h, go, dx, dgx, dga: [B,T,D] contiguous, `dtype`;  lam, dlam: [D] fp32.
+ * D must be a multiple of 64 (as the reference asserts, scan_fused.py:333); T >= 1.
+ * h0 / dh0: optional [B,D] fp32 (no counterpart in the reference, whose initial state is
+ * fixed at zero, scan_fused.py:77-79); pass NULL for the reference behaviour.
+ * The backward reads the forward OUTPUT h (as stored) for h_{t-1}, like the reference.
+ * Workspace (backward only): hawk_scan_bwd_workspace_bytes(B, D) bytes, 16-byte aligned.
+ * ---------------------------------------------------------------------------------------- */
+int hawk_scan_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                  void* h, int B, int T, int D, int dtype, void* stream);
+size_t hawk_scan_bwd_workspace_bytes(int B, int D);
+int hawk_scan_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                  const void* h, const void* go, void* dx, void* dgx, void* dga, float* dlam,
+                  float* dh0, void* workspace, size_t workspace_bytes, int B, int T, int D,
+                  int dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Causal depthwise temporal convolution, width W in [1,4].  Replaces Conv1D.forward
+ * (hawk/external.py:49-98) and the autograd backward of its eager ops.
+ *
+ *   y[b,t,d] = bias[d] + sum_{k<W} w[W-1-k, d] * x[b,t-k,d],   x[b,t<0] = 0.
+ *
+ * x: element (b,t,d) at x + b*x_batch_stride + t*x_row_stride + d (strides in ELEMENTS), so
+ * the strided half of the [B,T,2R] projection (hawk/hawk.py:164-166) is read in place.
+ * y, go: [B,T,D] contiguous.  dx is written with its own strides.  w: [W,D], bias: [D], fp32.
+ * D must be a multiple of 8; every base pointer 16-byte aligned; strides multiples of 8.
+ * Backward workspace: hawk_conv1d_bwd_workspace_bytes(B, T, D, W).
+ * ---------------------------------------------------------------------------------------- */
+int hawk_conv1d_fwd(const void* x, int64_t x_batch_stride, int64_t x_row_stride, const float* w,
+                    const float* bias, void* y, int B, int T, int D, int W, int in_dtype,
+                    int out_dtype, void* stream);
+size_t hawk_conv1d_bwd_workspace_bytes(int B, int T, int D, int W);
+int hawk_conv1d_bwd(const void* go, const void* x, int64_t x_batch_stride, int64_t x_row_stride,
+                    const float* w, void* dx, int64_t dx_batch_stride, int64_t dx_row_stride,
+                    float* dw, float* dbias, void* workspace, size_t workspace_bytes, int B, int T,
+                    int D, int W, int go_dtype, int x_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Cached single-token decode step of one Hawk block, any batch size.  Replaces the eager
+ * path hawk/hawk.py:168-179 (conv over [conv_state | x]) + hawk/cache.py:37-43 (roll), and
+ * hawk/hawk.py:137-151,193-198 (inference_prologue, h = a*state + x~, cache update).
+ *
+ * conv step : x_new [B,D] (row stride x_row_stride elements), conv_state [B,W-1,D] contiguous,
+ *             oldest row first, updated IN PLACE; y [B,D] contiguous.
+ * rglru step: x, gx, ga [B,D] contiguous `dtype`; state [B,D] `state_dtype`, updated IN PLACE
+ *             with h; h_out [B,D] `dtype` (may be NULL).
+ * ---------------------------------------------------------------------------------------- */
+int hawk_decode_conv_step(const void* x_new, int64_t x_row_stride, void* conv_state, const float* w,
+                          const float* bias, void* y, int B, int D, int W, int dtype,
+                          int state_dtype, void* stream);
+int hawk_decode_rglru_step(const void* x, const void* gx, const void* ga, const float* lam,
+                           void* state, void* h_out, int B, int D, int dtype, int state_dtype,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HAWK_B200_H_ */

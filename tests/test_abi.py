@@ -1,0 +1,72 @@
+"""The C-ABI library builds, loads and exports every symbol include/hawk_b200.h declares; its
+host-side argument validation answers without touching a GPU.  CPU only."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+import hawk_b200._lib as L
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "hawk_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hawk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = L.load()
+    names = _declared_symbols()
+    assert "hawk_scan_fwd" in names and "hawk_conv1d_bwd" in names
+    for n in names:
+        assert hasattr(lib, n), n
+    assert sorted(L.SIGNATURES) == names  # the ctypes table covers the header one to one
+    assert lib.hawk_version() == L.ABI_VERSION
+
+
+def test_strerror_is_total():
+    lib = L.load()
+    assert lib.hawk_strerror(0) == b"ok"
+    for code in range(-8, 0):
+        assert len(lib.hawk_strerror(code)) > 3
+    assert b"unknown" in lib.hawk_strerror(-99)
+
+
+def test_scan_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
+    assert lib.hawk_scan_fwd(None, p, p, p, None, p, 1, 8, 64, L.HAWK_BF16, None) == -1      # NULL
+    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 8, 96, L.HAWK_BF16, None) == -2         # D % 64
+    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 0, 64, L.HAWK_BF16, None) == -2         # T < 1
+    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 8, 64, 7, None) == -3                   # dtype
+    assert lib.hawk_scan_fwd(ctypes.c_void_p(4098), p, p, p, None, p, 1, 8, 64, L.HAWK_BF16, None) == -4
+    assert lib.hawk_scan_bwd_workspace_bytes(8, 2048) == 8 * 2048 * 4
+    args = [p] * 4 + [None] + [p] * 6 + [None]
+    assert lib.hawk_scan_bwd(*args, p, 16, 8, 16, 2048, L.HAWK_BF16, None) == -5             # workspace too small
+
+
+def test_conv_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)
+    assert lib.hawk_conv1d_fwd(p, 0, 64, p, p, p, 1, 8, 64, 5, 1, 1, None) == -7   # width 5 unsupported
+    assert lib.hawk_conv1d_fwd(p, 0, 64, p, p, p, 1, 8, 60, 4, 1, 1, None) == -2   # D % 8
+    assert lib.hawk_conv1d_fwd(p, 0, 68, p, p, p, 1, 8, 64, 4, 1, 1, None) == -4   # row stride % 8
+    assert lib.hawk_conv1d_bwd_workspace_bytes(8, 4096, 2048, 4) == 8 * 16 * 5 * 2048 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        L.load()
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from hawk_b200 import fused_linear_scan
+    x = torch.zeros(1, 4, 64)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fused_linear_scan(x, x, x, torch.zeros(64))

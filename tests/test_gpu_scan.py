@@ -1,0 +1,190 @@
+"""Parity of the CUDA RG-LRU scan (through the C ABI) with the CPU oracle.
+
+Tolerances (norm-wise; element-wise relative error is meaningless at zero crossings):
+  fp32 storage : rel-L2 and max-abs/max-abs <= 1e-5 against the fp64 oracle;
+  bf16 storage : <= 2e-2 against the fp64 oracle run on the same bf16-rounded inputs.
+"""
+import pytest
+import torch
+
+from conftest import load_golden, max_rel, rel_l2
+from oracle import scan as oscan
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+BF16_TOL = 2e-2
+
+
+def _inputs(B, T, D, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    x, gx, ga, go = (scale * torch.randn(B, T, D, generator=g) for _ in range(4))
+    lam = oscan.rnn_param_ring(D, generator=g)
+    if dtype != torch.float32:  # the oracle sees exactly the values the kernel sees
+        x, gx, ga, go = (t.to(dtype).float() for t in (x, gx, ga, go))
+    return x, gx, ga, go, lam
+
+
+def _run_gpu(x, gx, ga, go, lam, dtype, h0=None):
+    from hawk_b200 import fused_linear_scan
+    dev = "cuda:0"
+    xs = [t.to(dev, dtype).requires_grad_(True) for t in (x, gx, ga)]
+    lam_d = lam.to(dev).requires_grad_(True)
+    h0_d = None if h0 is None else h0.to(dev).requires_grad_(True)
+    h = fused_linear_scan(*xs, lam_d, h0=h0_d)
+    assert h.dtype == dtype and h.shape == x.shape
+    h.backward(go.to(dev, dtype))
+    outs = [h.detach()] + [t.grad for t in xs] + [lam_d.grad]
+    if h0 is not None:
+        outs.append(h0_d.grad)
+    return [o.float().cpu() for o in outs]
+
+
+def _oracle(x, gx, ga, go, lam, h_stored):
+    h = oscan.rglru_scan_fwd(x, gx, ga, lam, compute=torch.float64)
+    # the backward reads the h that was actually stored (rounded), as the reference does
+    grads = oscan.rglru_scan_bwd(x, gx, ga, lam, h_stored.double(), go, compute=torch.float64)
+    return (h,) + grads
+
+
+def _check(got, want, tol, names=("h", "dx", "dgx", "dga", "dlam")):
+    for n, a, b in zip(names, got, want):
+        assert rel_l2(a, b) <= tol, (n, rel_l2(a, b))
+        assert max_rel(a, b) <= tol, (n, max_rel(a, b))
+
+
+SHAPES = [(1, 1, 64), (1, 2, 64), (2, 3, 128), (2, 31, 64), (2, 32, 64), (2, 33, 64), (1, 63, 128), (1, 64, 128),
+          (1, 65, 128), (3, 257, 192), (2, 2048, 512), (1, 1000, 4096)]
+
+
+@pytest.mark.parametrize("B,T,D", SHAPES)
+def test_scan_fp32_matches_oracle(B, T, D):
+    x, gx, ga, go, lam = _inputs(B, T, D, seed=B * 1000 + T + D)
+    got = _run_gpu(x, gx, ga, go, lam, torch.float32)
+    _check(got, _oracle(x, gx, ga, go, lam, got[0]), FP32_TOL)
+
+
+@pytest.mark.parametrize("B,T,D", SHAPES)
+def test_scan_bf16_matches_oracle(B, T, D):
+    x, gx, ga, go, lam = _inputs(B, T, D, seed=7 + B * 1000 + T + D, dtype=torch.bfloat16)
+    got = _run_gpu(x, gx, ga, go, lam, torch.bfloat16)
+    _check(got, _oracle(x, gx, ga, go, lam, got[0]), BF16_TOL)
+
+
+def test_scan_config0_fp32():
+    """B=2, T=2048, D=512, fp32, h0=0, Lambda on the 0.9..0.999 ring, seed 0."""
+    torch.manual_seed(0)
+    x, gx, ga, go = (torch.randn(2, 2048, 512) for _ in range(4))
+    lam = oscan.rnn_param_ring(512)
+    got = _run_gpu(x, gx, ga, go, lam, torch.float32)
+    want = _oracle(x, gx, ga, go, lam, got[0])
+    _check(got, want, FP32_TOL)
+    assert max_rel(got[0][:, -1], want[0][:, -1]) <= FP32_TOL  # final state h_T = h[:, -1]
+
+
+def test_scan_extreme_gates_hit_sqrt_grad_clamp():
+    """Gate pre-activations of +-20 saturate a -> 1, where the reference clamps d sqrt (scan_fused.py:10-15)."""
+    x, gx, ga, go, lam = _inputs(2, 96, 64, seed=11, scale=8.0)
+    ga[:, ::3] = -20.0
+    gx[:, 1::3] = 20.0
+    got = _run_gpu(x, gx, ga, go, lam, torch.float32)
+    assert all(torch.isfinite(t).all() for t in got)
+    # 1 - a^2 cancels catastrophically in fp32 when a -> 1; the fp32 oracle has the same arithmetic
+    h32 = oscan.rglru_scan_fwd(x, gx, ga, lam)
+    g32 = oscan.rglru_scan_bwd(x, gx, ga, lam, got[0], go)
+    _check(got, (h32,) + g32, 2e-4)
+
+
+def test_scan_closed_form_known_answer():
+    lam = oscan.rnn_param_ring(64, generator=torch.Generator().manual_seed(3))
+    T = 700
+    ones, zeros = torch.ones(1, T, 64), torch.zeros(1, T, 64)
+    got = _run_gpu(ones, zeros, zeros, zeros, lam, torch.float32)
+    assert max_rel(got[0], oscan.closed_form_kat(lam, T)) <= FP32_TOL
+
+
+def test_scan_matches_reference_triton_golden():
+    """Against outputs of the reference's own kernels (bf16-truncating stores): within bf16 rounding."""
+    g = load_golden("scan_triton_interp.npz")
+    for tag in "abc":
+        x, gx, ga, go, lam = (g[f"{tag}_{k}"] for k in ("x", "gx", "ga", "go", "lam"))
+        if x.shape[1] < 2:
+            continue
+        got = _run_gpu(x, gx, ga, go, lam, torch.float32)
+        for n, a in zip(("h", "dx", "dgx", "dga", "dlam"), got):
+            assert max_rel(a, g[f"{tag}_{n}"]) <= 2e-2, (tag, n)
+
+
+def test_scan_autocast_casts_like_the_reference():
+    from hawk_b200 import fused_linear_scan
+    x, gx, ga, go, lam = _inputs(2, 40, 64, seed=5)
+    xs = [t.cuda().requires_grad_(True) for t in (x, gx, ga)]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        h = fused_linear_scan(*xs, lam.cuda())
+    assert h.dtype == torch.bfloat16
+    h.float().sum().backward()
+    assert all(t.grad.dtype == torch.float32 for t in xs)
+    want = oscan.rglru_scan_fwd(*(t.bfloat16().float() for t in (x, gx, ga)), lam, compute=torch.float64)
+    assert rel_l2(h.float().cpu(), want) <= BF16_TOL
+
+
+def test_scan_noncontiguous_inputs_and_initial_state():
+    x, gx, ga, go, lam = _inputs(2, 70, 128, seed=9)
+    h0 = torch.randn(2, 128, generator=torch.Generator().manual_seed(1))
+    big = torch.randn(2, 70, 256)
+    big[..., :128] = x
+    from hawk_b200 import fused_linear_scan
+    hv = fused_linear_scan(big.cuda()[..., :128], gx.cuda(), ga.cuda(), lam.cuda())
+    assert rel_l2(hv.cpu(), oscan.rglru_scan_fwd(x, gx, ga, lam, compute=torch.float64)) <= FP32_TOL
+    got = _run_gpu(x, gx, ga, go, lam, torch.float32, h0=h0)
+    ref = oscan.rglru_scan_autograd  # differentiable fp64 statement, extended with h0 below
+    xs = [t.double().requires_grad_(True) for t in (x, gx, ga, lam, h0)]
+    sp = torch.nn.functional.softplus(xs[3])
+    a = torch.exp(-8.0 * torch.sigmoid(xs[2]) * sp)
+    beta = xs[0] * torch.sigmoid(xs[1]) * torch.sqrt(1 - a * a)
+    hs, st = [], xs[4]
+    for t in range(x.shape[1]):
+        st = a[:, t] * st + beta[:, t]
+        hs.append(st)
+    h = torch.stack(hs, 1)
+    grads = torch.autograd.grad(h, xs, go.double())
+    _check(got, (h.detach(),) + grads, FP32_TOL, names=("h", "dx", "dgx", "dga", "dlam", "dh0"))
+
+
+def test_scan_is_deterministic():
+    x, gx, ga, go, lam = _inputs(4, 300, 256, seed=21, dtype=torch.bfloat16)
+    a = _run_gpu(x, gx, ga, go, lam, torch.bfloat16)
+    b = _run_gpu(x, gx, ga, go, lam, torch.bfloat16)
+    assert all(torch.equal(p, q) for p, q in zip(a, b))
+
+
+def test_scan_metric_shape_properties():
+    """B=8, T=4096, D=2048 bf16 (too large for the CPU oracle in seconds): size-independent checks.
+    (1) time-locality: h[:, :t] does not depend on inputs after t; (2) a channel slice scanned alone
+    gives the same bits; (3) a sampled set of channels matches the fp64 oracle."""
+    from hawk_b200 import fused_linear_scan
+    B, T, D = 8, 4096, 2048
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x, gx, ga, go = (torch.randn(B, T, D, generator=g, device="cuda").bfloat16() for _ in range(4))
+    lam = oscan.rnn_param_ring(D, generator=torch.Generator().manual_seed(0)).cuda()
+    xs = [t.clone().requires_grad_(True) for t in (x, gx, ga)]
+    lam_r = lam.clone().requires_grad_(True)
+    h = fused_linear_scan(*xs, lam_r)
+    h.backward(go)
+    # (1)
+    h_half = fused_linear_scan(x[:, :1000].contiguous(), gx[:, :1000].contiguous(), ga[:, :1000].contiguous(), lam)
+    assert torch.equal(h_half, h[:, :1000])
+    # (2)
+    sl = slice(640, 704)
+    h_sl = fused_linear_scan(x[..., sl].contiguous(), gx[..., sl].contiguous(), ga[..., sl].contiguous(), lam[sl].contiguous())
+    assert torch.equal(h_sl, h[..., sl])
+    # (3)
+    idx = torch.tensor([0, 1, 63, 64, 777, 1024, 2046, 2047])
+    cx, cgx, cga, cgo = (t[:2][..., idx.cuda()].float().cpu() for t in (x, gx, ga, go))
+    hs = h.detach()[:2][..., idx.cuda()].float().cpu()
+    want_h = oscan.rglru_scan_fwd(cx, cgx, cga, lam.cpu()[idx], compute=torch.float64)
+    assert rel_l2(hs, want_h) <= BF16_TOL
+    wdx, wdgx, wdga, _ = oscan.rglru_scan_bwd(cx, cgx, cga, lam.cpu()[idx], hs.double(), cgo, compute=torch.float64)
+    for a, b in zip((xs[0].grad, xs[1].grad, xs[2].grad), (wdx, wdgx, wdga)):
+        assert rel_l2(a[:2][..., idx.cuda()].float().cpu(), b) <= BF16_TOL
+    assert torch.isfinite(lam_r.grad).all()
