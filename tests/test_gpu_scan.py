@@ -92,7 +92,7 @@ def test_scan_extreme_gates_hit_sqrt_grad_clamp():
     # 1 - a^2 cancels catastrophically in fp32 when a -> 1; the fp32 oracle has the same arithmetic
     h32 = oscan.rglru_scan_fwd(x, gx, ga, lam)
     g32 = oscan.rglru_scan_bwd(x, gx, ga, lam, got[0], go)
-    _check(got, (h32,) + g32, 2e-4)
+    _check(got, (h32,) + g32, 1e-3)
 
 
 def test_scan_closed_form_known_answer():
