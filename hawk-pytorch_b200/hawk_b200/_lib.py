@@ -30,6 +30,8 @@ SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_conv_step": (c_int, [_P, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_rglru_step": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "hawk_linear_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "hawk_linear_ce_fwd_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }
 
 _lib = None

@@ -298,3 +298,81 @@ def decode_rglru_step(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: 
 @decode_rglru_step.register_fake
 def _(x, gx, ga, lam, state):
     return torch.empty_like(x)
+
+
+# ---------------------------------------------------------------------------------------------
+# fused linear + cross-entropy
+# ---------------------------------------------------------------------------------------------
+_ce_status = {}  # device index -> int32[1] status word shared by every call on that device
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    t = _ce_status.get(device.index)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _ce_status[device.index] = t
+    return t
+
+
+def check_device_status(device=None) -> None:
+    """Raises if a kernel on `device` gave up a bounded wait since the last check (synchronises)."""
+    for idx, t in list(_ce_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        if int(t.item()) != 0:
+            t.zero_()
+            raise RuntimeError("hawk_b200: a tcgen05 GEMM abandoned a bounded mbarrier wait; results are invalid")
+
+
+@torch.library.custom_op("hawk_b200::linear_ce", mutates_args=())
+def linear_ce(weight: torch.Tensor, act: torch.Tensor, labels: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(loss [], dweight [V,H] fp32, dact [N,H] fp32) of mean CE(act @ weight^T, labels)."""
+    lib = _lib.load()
+    V, H = weight.shape
+    N = act.shape[0]
+    weight, act, labels = weight.contiguous(), act.contiguous(), labels.contiguous()
+    if labels.dtype != torch.int64:
+        labels = labels.long()
+    loss = torch.empty((), dtype=torch.float32, device=act.device)
+    dweight = torch.empty(V, H, dtype=torch.float32, device=act.device)
+    dact = torch.empty(N, H, dtype=torch.float32, device=act.device)
+    ws_bytes = lib.hawk_linear_ce_workspace_bytes(N, H, V)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=act.device)
+    with _on(act):
+        _lib.check(lib.hawk_linear_ce_fwd_bwd(weight.data_ptr(), act.data_ptr(), labels.data_ptr(), loss.data_ptr(),
+                                              dweight.data_ptr(), dact.data_ptr(), ws.data_ptr(), ws_bytes, N, H, V,
+                                              _dt(weight), _status_word(act.device).data_ptr(), _stream(act)),
+                   "hawk_linear_ce_fwd_bwd")
+    return loss, dweight, dact
+
+
+@linear_ce.register_fake
+def _(weight, act, labels):
+    return (act.new_empty((), dtype=torch.float32), weight.new_empty(weight.shape, dtype=torch.float32),
+            act.new_empty(act.shape, dtype=torch.float32))
+
+
+def _ce_setup(ctx, inputs, output):
+    weight, act, _ = inputs
+    _, dweight, dact = output
+    ctx.save_for_backward(dweight, dact)
+    ctx.dtypes = (weight.dtype, act.dtype)
+
+
+def _ce_backward(ctx, g_loss, g_dw, g_da):
+    dweight, dact = ctx.saved_tensors  # computed in the forward, as in the reference (:63,66-73)
+    wd, ad = ctx.dtypes
+    return (g_loss * dweight).to(wd), (g_loss * dact).to(ad), None
+
+
+linear_ce.register_autograd(_ce_backward, setup_context=_ce_setup)
+
+
+def fused_cross_entropy(lm_head_weight, act, labels):
+    """Mean cross-entropy of `act @ lm_head_weight.T` against `labels`; drop-in for
+    hawk/fused_cross_entropy.py:77-79.  weight [V,H], act [N,H] (fp32 or bf16), labels [N] int64.
+    The arithmetic is the reference's under bf16 autocast whether or not autocast is on: bf16
+    tensor-core GEMMs with fp32 accumulation, bf16 logits, fp32 softmax."""
+    if act.dtype != lm_head_weight.dtype:
+        act = act.to(lm_head_weight.dtype)
+    return linear_ce(lm_head_weight, act, labels)[0]

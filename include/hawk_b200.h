@@ -110,6 +110,26 @@ int hawk_decode_rglru_step(const void* x, const void* gx, const void* ga, const 
                            void* state, void* h_out, int B, int D, int dtype, int state_dtype,
                            void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Fused linear + cross-entropy.  Replaces CrossEntropyLoopedFused.forward
+ * (hawk/fused_cross_entropy.py:13-64): mean cross-entropy of act @ weight^T against labels, and
+ * BOTH gradients, in one call (the reference also computes them in its forward, :47-61; its
+ * backward only scales them, :66-73).
+ *
+ * weight [V,H], act [N,H]: contiguous, `dtype` (HAWK_F32 or HAWK_BF16); labels [N] int64 in [0,V).
+ * loss: one fp32; dweight [V,H] and dact [N,H]: fp32, already scaled by 1/N.
+ * Arithmetic is what the reference does under bf16 autocast: bf16 operands, fp32 accumulation,
+ * logits rounded to bf16, softmax in fp32, dprobs rounded to bf16 before the gradient GEMMs.
+ * H must be a multiple of 8.  Workspace: hawk_linear_ce_workspace_bytes(N, H, V), 256-byte aligned
+ * (bf16 operand copies, the [N,V] bf16 logits/dprobs buffer and its transpose, row statistics).
+ * status: one int32 in device memory, zeroed by the caller once; a kernel whose bounded wait on an
+ * mbarrier ran out sets it to 1 (the results of that call are then invalid) instead of hanging.
+ * ---------------------------------------------------------------------------------------- */
+size_t hawk_linear_ce_workspace_bytes(int64_t N, int64_t H, int64_t V);
+int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const int64_t* labels, float* loss,
+                           float* dweight, float* dact, void* workspace, size_t workspace_bytes,
+                           int64_t N, int64_t H, int64_t V, int dtype, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
