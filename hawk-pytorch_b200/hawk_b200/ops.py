@@ -44,22 +44,64 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-class _on:
-    """Makes the tensor's device current for the duration of a launch (no-op when it already is)."""
+class KernelLog:
+    """Counts the kernels this library launches and, on request, brackets every C-ABI call with CUDA
+    events on the launching stream (how the benchmark measures kernel time inside a training step)."""
 
-    def __init__(self, t):
+    def __init__(self):
+        self.enabled = False
+        self.timed = False
+        self.counts = {}
+        self.events = {}
+
+    def reset(self, enabled: bool = True, timed: bool = False) -> None:
+        self.enabled, self.timed = enabled, timed
+        self.counts, self.events = {}, {}
+
+    def total_launches(self) -> int:
+        return sum(self.counts.values())
+
+    def mean_ms(self, name: str) -> Optional[float]:
+        """Mean device time of one call of `name` (call after torch.cuda.synchronize())."""
+        ev = self.events.get(name)
+        if not ev:
+            return None
+        return sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+
+
+LOG = KernelLog()
+
+
+class _on:
+    """Makes the tensor's device current for the duration of a C-ABI call (no-op when it already is)
+    and reports the call to LOG: `name` is the entry point, `kernels` how many kernels it launches."""
+
+    def __init__(self, t, name: str = "", kernels: int = 0):
         if not t.is_cuda:
             raise RuntimeError("hawk_b200: tensors must be on a CUDA device (there is no CPU path)")
         self.idx = t.device.index
         self.prev = None
+        self.name, self.kernels = name, kernels
+        self.stream = None
+        self.start = None
 
     def __enter__(self):
         cur = torch.cuda.current_device()
         if self.idx is not None and self.idx != cur:
             self.prev = cur
             torch.cuda.set_device(self.idx)
+        if LOG.enabled and self.name:
+            LOG.counts[self.name] = LOG.counts.get(self.name, 0) + self.kernels
+            if LOG.timed:
+                self.stream = torch.cuda.current_stream()
+                self.start = torch.cuda.Event(enable_timing=True)
+                self.start.record(self.stream)
 
     def __exit__(self, *a):
+        if self.start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(self.stream)
+            LOG.events.setdefault(self.name, []).append((self.start, end))
         if self.prev is not None:
             torch.cuda.set_device(self.prev)
 
@@ -76,7 +118,7 @@ def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
     if h0 is not None:
         h0 = h0.contiguous()
     h = torch.empty_like(x)
-    with _on(x):
+    with _on(x, "scan_fwd", 1):
         _lib.check(lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
                                      h.data_ptr(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd")
     return h
@@ -102,7 +144,7 @@ def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     if h0 is not None:
         h0 = h0.contiguous()
-    with _on(x):
+    with _on(x, "scan_bwd", 2):
         _lib.check(lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
                                      h.data_ptr(), go.data_ptr(), dx.data_ptr(), dgx.data_ptr(), dga.data_ptr(),
                                      dlam.data_ptr(), dh0.data_ptr(), ws.data_ptr(), ws_bytes, B, T, D, _dt(x),
@@ -169,7 +211,7 @@ def conv1d_fwd(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, out_dtype: tor
     xv = _conv_view(x)
     w, b = w.contiguous(), b.contiguous()
     y = torch.empty(B, T, D, dtype=out_dtype, device=x.device)
-    with _on(x):
+    with _on(x, "conv1d_fwd", 1):
         _lib.check(lib.hawk_conv1d_fwd(xv.data_ptr(), xv.stride(0), xv.stride(1), w.data_ptr(), b.data_ptr(),
                                        y.data_ptr(), B, T, D, w.shape[0], _dt(xv), _DT[out_dtype], _stream(x)),
                    "hawk_conv1d_fwd")
@@ -193,7 +235,7 @@ def conv1d_bwd(go: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> Tuple[torc
     db = torch.empty(D, dtype=torch.float32, device=x.device)
     ws_bytes = lib.hawk_conv1d_bwd_workspace_bytes(B, T, D, W)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-    with _on(x):
+    with _on(x, "conv1d_bwd", 2):
         _lib.check(lib.hawk_conv1d_bwd(go.data_ptr(), xv.data_ptr(), xv.stride(0), xv.stride(1), w.data_ptr(),
                                        dx.data_ptr(), dx.stride(0), dx.stride(1), dw.data_ptr(), db.data_ptr(),
                                        ws.data_ptr(), ws_bytes, B, T, D, W, _dt(go), _dt(xv), _stream(x)),
@@ -267,7 +309,7 @@ def decode_conv_step(x_new: torch.Tensor, conv_state: torch.Tensor, w: torch.Ten
         x_new = x_new.contiguous()
     assert conv_state.is_contiguous() and conv_state.shape == (B, w.shape[0] - 1, D)
     y = torch.empty(B, D, dtype=x_new.dtype, device=x_new.device)
-    with _on(x_new):
+    with _on(x_new, "decode_conv_step", 1):
         _lib.check(lib.hawk_decode_conv_step(x_new.data_ptr(), x_new.stride(0), conv_state.data_ptr(), w.data_ptr(),
                                              b.data_ptr(), y.data_ptr(), B, D, w.shape[0], _dt(x_new),
                                              _dt(conv_state), _stream(x_new)), "hawk_decode_conv_step")
@@ -288,7 +330,7 @@ def decode_rglru_step(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: 
     x, gx, ga = x.contiguous(), gx.contiguous(), ga.contiguous()
     assert state.is_contiguous() and state.shape == (B, D)
     h = torch.empty_like(x)
-    with _on(x):
+    with _on(x, "decode_rglru_step", 1):
         _lib.check(lib.hawk_decode_rglru_step(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(),
                                               state.data_ptr(), h.data_ptr(), B, D, _dt(x), _dt(state), _stream(x)),
                    "hawk_decode_rglru_step")
@@ -338,7 +380,7 @@ def linear_ce(weight: torch.Tensor, act: torch.Tensor, labels: torch.Tensor) -> 
     dact = torch.empty(N, H, dtype=torch.float32, device=act.device)
     ws_bytes = lib.hawk_linear_ce_workspace_bytes(N, H, V)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=act.device)
-    with _on(act):
+    with _on(act, "linear_ce", 8):
         _lib.check(lib.hawk_linear_ce_fwd_bwd(weight.data_ptr(), act.data_ptr(), labels.data_ptr(), loss.data_ptr(),
                                               dweight.data_ptr(), dact.data_ptr(), ws.data_ptr(), ws_bytes, N, H, V,
                                               _dt(weight), _status_word(act.device).data_ptr(), _stream(act)),

@@ -176,3 +176,31 @@ def decode_step(sd, token_ids, caches, *, state_dtype=torch.bfloat16):
         new_caches.append(dict(recc=h.to(state_dtype), conv=conv_state))
     logits = F.linear(rms_norm(x, sd["norm.weight"]), sd["lm_head.weight"])
     return logits[:, None], new_caches
+
+
+def random_state_dict(vocab, hidden, intermediate, layers, recurrent, num_blocks, conv_width, *, seed=0):
+    """A reference-format state dict drawn with the reference's initialisation families
+    (hawk/hawk.py:77-79,124-132,256-258; hawk/external.py:45-47,153-168,214-222): LeCun normal for the
+    embedding, input_xy and gate_up_proj; zeros for lm_head and both resid_proj; ring init for Lambda;
+    N(0, 0.01/width) conv taps; N(0, 1/bw) gate blocks; zero biases; unit norm weights."""
+    from .scan import rnn_param_ring
+    g = torch.Generator().manual_seed(seed)
+    n = lambda *shape, std: torch.randn(*shape, generator=g) * std
+    bw = recurrent // num_blocks
+    sd = {"embed_tokens.weight": n(vocab, hidden, std=hidden ** -0.5), "norm.weight": torch.ones(hidden),
+          "lm_head.weight": torch.zeros(vocab, hidden)}
+    for i in range(layers):
+        p = f"layers.{i}."
+        sd[p + "recc.rg_lru_a_param"] = rnn_param_ring(recurrent, generator=g)
+        sd[p + "recc.input_xy.weight"] = n(2 * recurrent, hidden, std=hidden ** -0.5)
+        for gate in ("rg_lru_input_gate", "rg_lru_a_gate"):
+            sd[p + f"recc.{gate}.w"] = n(num_blocks, bw, bw, std=bw ** -0.5)
+            sd[p + f"recc.{gate}.b"] = torch.zeros(num_blocks, bw)
+        sd[p + "recc.resid_proj.weight"] = torch.zeros(hidden, recurrent)
+        sd[p + "recc.conv1d.w"] = n(conv_width, recurrent, std=(0.01 / conv_width) ** 0.5)
+        sd[p + "recc.conv1d.b"] = torch.zeros(recurrent)
+        sd[p + "mlp.gate_up_proj.weight"] = n(2 * intermediate, hidden, std=hidden ** -0.5)
+        sd[p + "mlp.resid_proj.weight"] = torch.zeros(hidden, intermediate)
+        sd[p + "input_norm.weight"] = torch.ones(hidden)
+        sd[p + "post_recurrent_norm.weight"] = torch.ones(hidden)
+    return sd
