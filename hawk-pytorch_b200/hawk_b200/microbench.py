@@ -1,0 +1,117 @@
+"""Times one operator of this library in isolation (CUDA events, median of N launches).
+
+    python -m hawk_b200.microbench scan      [--B 8 --T 4096 --D 2048 --dtype bf16]
+    python -m hawk_b200.microbench conv1d    [--B 8 --T 4096 --D 2048 --dtype bf16]
+    python -m hawk_b200.microbench linear_ce [--N 32760 --H 2048 --V 32000]
+    python -m hawk_b200.microbench decode    [--B 256 --D 2048 --layers 24]
+
+Prints one JSON line per kernel with the achieved rate against its algorithmic work:
+scan 8 (forward) / 16 (backward) bytes per element in bf16, conv1d 4 / 6, linear_ce 6*N*H*V flop,
+decode 8*B*D*elem bytes per step.  Inputs are seeded normal draws; Lambda sits on the reference's
+0.9..0.999 ring.  Working sets beyond the 126 MB L2 need no flush between launches; smaller ones
+are bracketed by a flush write (`--flush`).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from . import ops
+from .model import ring_init_
+
+
+def _time(fn, iters, warmup, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _emit(name, ms, work, unit, **extra):
+    rate = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+    print(json.dumps({"kernel": name, "ms": round(ms, 5), "rate": round(rate, 1), "unit": unit, **extra}), flush=True)
+    return rate
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "decode"])
+    ap.add_argument("--B", type=int, default=8)
+    ap.add_argument("--T", type=int, default=4096)
+    ap.add_argument("--D", type=int, default=2048)
+    ap.add_argument("--N", type=int, default=8 * 4095)
+    ap.add_argument("--H", type=int, default=2048)
+    ap.add_argument("--V", type=int, default=32000)
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--flush", action="store_true")
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    dt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    es = 2 if a.dtype == "bf16" else 4
+    g = torch.Generator(device="cuda").manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
+    shape = {"B": a.B, "T": a.T, "D": a.D, "dtype": a.dtype}
+
+    if a.op == "scan":
+        x, gx, ga, go = (torch.randn(a.B, a.T, a.D, generator=g, device=dev).to(dt) for _ in range(4))
+        lam = ring_init_(torch.empty(a.D)).to(dev)
+        n = a.B * a.T * a.D
+        h = ops.scan_fwd(x, gx, ga, lam, None)
+        tf = _time(lambda: ops.scan_fwd(x, gx, ga, lam, None), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.scan_bwd(x, gx, ga, lam, None, h, go), a.iters, a.warmup, flush)
+        _emit("scan_fwd", tf, 4 * es * n, "GB/s", **shape)
+        _emit("scan_bwd", tb, 8 * es * n, "GB/s", **shape)
+        _emit("scan_fwd+bwd", tf + tb, 12 * es * n, "GB/s", **shape)
+    elif a.op == "conv1d":
+        xy = torch.randn(a.B, a.T, 2 * a.D, generator=g, device=dev).to(dt)
+        xv = xy[..., :a.D]  # the strided half the model passes
+        go = torch.randn(a.B, a.T, a.D, generator=g, device=dev).to(dt)
+        w, b = torch.randn(4, a.D, device=dev) * 0.05, torch.zeros(a.D, device=dev)
+        n = a.B * a.T * a.D
+        tf = _time(lambda: ops.conv1d_fwd(xv, w, b, dt), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.conv1d_bwd(go, xv, w), a.iters, a.warmup, flush)
+        _emit("conv1d_fwd", tf, 2 * es * n, "GB/s", **shape)
+        _emit("conv1d_bwd", tb, 3 * es * n, "GB/s", **shape)
+    elif a.op == "linear_ce":
+        w = torch.randn(a.V, a.H, generator=g, device=dev) / math.sqrt(a.H)
+        act = torch.randn(a.N, a.H, generator=g, device=dev)
+        lab = torch.randint(0, a.V, (a.N,), generator=g, device=dev)
+        t = _time(lambda: ops.linear_ce(w, act, lab), max(3, a.iters // 4), 2, flush)
+        ops.check_device_status()
+        _emit("linear_ce", t, 6 * a.N * a.H * a.V, "TFLOP/s", N=a.N, H=a.H, V=a.V)
+    else:
+        x, gx, ga = (torch.randn(a.B, a.D, generator=g, device=dev).to(dt) for _ in range(3))
+        xy = torch.randn(a.B, 2 * a.D, generator=g, device=dev).to(dt)
+        lam = ring_init_(torch.empty(a.D)).to(dev)
+        w, b = torch.randn(4, a.D, device=dev) * 0.05, torch.zeros(a.D, device=dev)
+        states = [torch.randn(a.B, a.D, generator=g, device=dev).to(dt) for _ in range(a.layers)]
+        convs = [torch.randn(a.B, 3, a.D, generator=g, device=dev).to(dt) for _ in range(a.layers)]
+
+        def step():
+            for s, c in zip(states, convs):
+                ops.decode_conv_step(xy[:, :a.D], c, w, b)
+                ops.decode_rglru_step(x, gx, ga, lam, s)
+        t = _time(step, a.iters, a.warmup, flush)
+        _emit("decode_conv+rglru_step", t / a.layers, 8 * a.B * a.D * es, "GB/s", B=a.B, D=a.D, layers=a.layers,
+              dtype=a.dtype)
+
+
+if __name__ == "__main__":
+    main()
