@@ -24,10 +24,12 @@ from .model import ring_init_
 
 
 def _time(fn, iters, warmup, flush=None):
+    """Median device time of one launch.  Launches are queued back to back and bracketed pairwise by
+    events, so the stream never runs dry (an idle stream would add host launch latency to the interval)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    ts = []
+    evs = []
     for _ in range(iters):
         if flush is not None:
             flush.zero_()
@@ -35,9 +37,9 @@ def _time(fn, iters, warmup, flush=None):
         a.record()
         fn()
         b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
-    ts.sort()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
     return ts[len(ts) // 2]
 
 
@@ -50,7 +52,7 @@ def _emit(name, ms, work, unit, **extra):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "decode"])
-    ap.add_argument("--B", type=int, default=8)
+    ap.add_argument("--B", type=int, default=None)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--D", type=int, default=2048)
     ap.add_argument("--N", type=int, default=8 * 4095)
@@ -62,6 +64,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--flush", action="store_true")
     a = ap.parse_args(argv)
+    if a.B is None:
+        a.B = 256 if a.op == "decode" else 8
     dev = torch.device("cuda")
     dt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     es = 2 if a.dtype == "bf16" else 4
