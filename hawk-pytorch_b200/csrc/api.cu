@@ -14,6 +14,7 @@ extern "C" const char* hawk_strerror(int status) {
     case HAWK_ERR_LAUNCH: return "CUDA refused a kernel launch";
     case HAWK_ERR_UNSUPPORTED: return "request not supported by this build";
     case HAWK_ERR_DEVICE: return "wrong device or driver entry point unavailable";
+    case HAWK_ERR_TOO_LARGE: return "size exceeds the built-in scratch of the no-allocation entry point (B*D <= 262144)";
     default: return "unknown hawk_status";
   }
 }

@@ -19,6 +19,7 @@
 // c_t = a_t * dh_t:   dh_t = go_t + c_{t+1},   c_t = a_t * dh_t,
 // which only needs row-local coefficients.  All outputs are dh_t times row-local factors.
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -623,4 +624,58 @@ extern "C" int hawk_scan_bwd(const void* x, const void* gx, const void* ga, cons
     default: HAWK_BWD(float, 2, 4, 8, 4, 4, false);
   }
 #undef HAWK_BWD
+}
+
+// ----------------------------------------------------------------------------------------------
+// Backward without a caller-supplied workspace.
+//
+// Some hosts must not touch the CUDA allocator once they are running: a serving process that handed
+// all device memory to its own arena at start-up and has no slack left to carve a workspace from, or
+// a latency-critical loop that cannot afford cudaMalloc's device-wide synchronisation.  For them the
+// [B,D] fp32 scratch of the Lambda-gradient reduction lives in a fixed array inside this library
+// (1 MiB per GPU that loads it, held until the process exits).
+//
+// In host code the array's NAME is only a stand-in symbol, not a device address; the address comes
+// from cudaGetSymbolAddress, asked once per device with that device current, and is what the
+// kernels receive.  That look-up happens inside the first call on each device, so make that first
+// call outside any stream capture.  All calls on a device share the one array and it keeps whatever
+// the previous call left: nothing in it needs zeroing (every (batch row, channel) entry that the
+// batch sum reads is rewritten by the scan kernel of the same call), but two calls that overlap on
+// the GPU (different streams) race on it.
+// ----------------------------------------------------------------------------------------------
+namespace hawk {
+constexpr long long kNoAllocMaxBD = 1LL << 18;  // B * D <= 262144 floats (1 MiB)
+static __device__ __align__(256) float g_scan_bwd_noalloc_scratch[kNoAllocMaxBD];
+
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_scratch_addr[kNoAllocMaxDevices];  // device address per device ordinal
+static std::mutex g_noalloc_mu;
+
+static int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return HAWK_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_scan_bwd_noalloc_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return HAWK_ERR_DEVICE;
+    }
+    g_noalloc_scratch_addr[dev] = p;
+  }
+  *out = g_noalloc_scratch_addr[dev];
+  return HAWK_OK;
+}
+}  // namespace hawk
+
+extern "C" int hawk_scan_bwd_noalloc(const void* x, const void* gx, const void* ga, const float* lam,
+                                     const float* h0, const void* h, const void* go, void* dx, void* dgx,
+                                     void* dga, float* dlam, float* dh0, int B, int T, int D, int dtype,
+                                     void* stream) {
+  if (B >= 1 && D >= 1 && (long long)B * (long long)D > hawk::kNoAllocMaxBD) return HAWK_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = hawk::noalloc_scratch_for_current_device(&scratch);
+  if (rc != HAWK_OK) return rc;
+  return hawk_scan_bwd(x, gx, ga, lam, h0, h, go, dx, dgx, dga, dlam, dh0, scratch,
+                       (size_t)hawk::kNoAllocMaxBD * sizeof(float), B, T, D, dtype, stream);
 }

@@ -24,6 +24,7 @@ SIGNATURES = {
     "hawk_scan_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
     "hawk_scan_bwd": (c_int, [_P] * 13 + [c_size_t, c_int, c_int, c_int, c_int, _P]),
+    "hawk_scan_bwd_noalloc": (c_int, [_P] * 12 + [c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_fwd": (c_int, [_P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "hawk_conv1d_bwd": (c_int, [_P, _P, c_int64, c_int64, _P, _P, c_int64, c_int64, _P, _P, _P, c_size_t,

@@ -41,7 +41,8 @@ typedef enum hawk_status {
   HAWK_ERR_WORKSPACE = -5,   /* workspace missing or too small */
   HAWK_ERR_LAUNCH = -6,      /* the CUDA runtime refused a launch (cudaGetLastError) */
   HAWK_ERR_UNSUPPORTED = -7, /* valid request this build does not implement */
-  HAWK_ERR_DEVICE = -8       /* wrong device / driver entry point unavailable */
+  HAWK_ERR_DEVICE = -8,      /* wrong device / driver entry point unavailable */
+  HAWK_ERR_TOO_LARGE = -9    /* size exceeds the built-in scratch of a *_noalloc entry point */
 } hawk_status;
 
 /* ABI version of the loaded library (HAWK_B200_ABI_VERSION at build time). */
@@ -71,6 +72,16 @@ int hawk_scan_bwd(const void* x, const void* gx, const void* ga, const float* la
                   const void* h, const void* go, void* dx, void* dgx, void* dga, float* dlam,
                   float* dh0, void* workspace, size_t workspace_bytes, int B, int T, int D,
                   int dtype, void* stream);
+
+/* hawk_scan_bwd for hosts that cannot allocate device memory (no counterpart in the reference, which
+ * allocates its scratch with torch.empty on every call, hawk/scan_fused.py:378).  Same arguments and
+ * results as hawk_scan_bwd but no workspace: the [B,D] fp32 scratch is a fixed 1 MiB array inside the
+ * library (per GPU, kept until exit), so B * D <= 262144 or HAWK_ERR_TOO_LARGE.  Calls nothing that
+ * allocates.  The first call on each device looks the array's device address up (make it outside a
+ * stream capture).  All calls on a device share the array: calls overlapping on the GPU race. */
+int hawk_scan_bwd_noalloc(const void* x, const void* gx, const void* ga, const float* lam,
+                          const float* h0, const void* h, const void* go, void* dx, void* dgx, void* dga,
+                          float* dlam, float* dh0, int B, int T, int D, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Causal depthwise temporal convolution, width W in [1,4].  Replaces Conv1D.forward
