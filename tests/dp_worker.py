@@ -1,0 +1,50 @@
+"""Worker of tests/test_dp_gloo.py: one data-parallel rank on CPU over gloo.  The product has no CPU
+kernels, so this TEST substitutes oracle statements for the three operators before training."""
+import os
+import sys
+
+import torch
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "hawk-pytorch_b200"))
+
+import hawk_b200.model as M  # noqa: E402
+from hawk_b200 import train  # noqa: E402
+from oracle import model as omodel  # noqa: E402
+
+
+def patch_ops():
+    M.ops.fused_linear_scan = lambda x, gx, ga, lam, h0=None: omodel.scan(x, gx, ga, lam)
+    M.ops.fused_cross_entropy = lambda w, a, l: F.cross_entropy(F.linear(a, w), l)
+    M.ops.Conv1D.forward = lambda self, x: omodel.conv1d(x, self.w, self.b)
+
+
+def make_trainer(world):
+    cfg = M.HawkConfig(64, 32, 64, 2, 32, 4, 4)
+    tr = train.Trainer(cfg, "cpu", seed=0, lr=1e-2, world_size=world, autocast=False)
+    sd = omodel.dezero(dict(tr.model.state_dict()), seed=1)  # so that every parameter gets a gradient
+    tr.model.load_state_dict(sd)
+    return tr
+
+
+def data(step):
+    g = torch.Generator().manual_seed(100 + step)
+    return torch.randint(1, 64, (4, 12), generator=g)  # the GLOBAL batch of this step
+
+
+if __name__ == "__main__":
+    out_path = sys.argv[1]
+    fail_rank = int(sys.argv[2]) if len(sys.argv) > 2 else -1
+    patch_ops()
+    rank, _, world = train.init_distributed("gloo")
+    tr = make_trainer(world)
+    losses = []
+    for step in range(3):
+        if rank == fail_rank and step == 1:
+            os._exit(17)  # a rank that dies between steps: the others must fail, not hang
+        ids = data(step).chunk(world, dim=0)[rank]  # batch sharding: rank r takes its slice
+        losses.append(float(tr.step(ids)))
+    torch.save({"losses": losses, "params": {k: v.detach().clone() for k, v in tr.model.state_dict().items()}},
+               f"{out_path}.{rank}")
