@@ -1,0 +1,300 @@
+// Pointwise / row-reduction glue of the Hawk block around the GEMMs, fused into single HBM passes:
+//   gelu_mul : out = gelu(a) * b            (hawk/hawk.py:134-135 gelu(y)*h, :82-86 gelu(gate)*up)
+//   rms_norm : y = x * rsqrt(mean(x^2)+eps) * w   (hawk/hawk.py:47-58), statistics in fp32
+// In eager PyTorch these are 2 and ~6 launches over [B*T, width] tensors each way, several of them on
+// strided chunk views (non-vectorised).  Here every tensor is read once and written once with 16-byte
+// accesses; a and b may be row-strided views (the halves of a projection output), and the backward of
+// gelu_mul can write both gradients into the two halves of one buffer, so no concatenation is needed.
+#include "common.cuh"
+
+namespace hawk {
+
+// exact (erf) GELU, as torch.nn.functional.gelu's default
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ void gelu_and_grad(float x, float& g, float& dg) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  g = x * cdf;
+  dg = cdf + x * pdf;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_mul_fwd_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ b, int64_t ldb, T* __restrict__ out,
+                    int64_t ldo, int64_t M, int J) {
+  constexpr int VEC = 8;
+  const int nvec = J / VEC;
+  const int64_t total = M * nvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / nvec;
+    const int j = (int)(i % nvec) * VEC;
+    float av[VEC], bv[VEC], ov[VEC];
+    VecIO<T, VEC>::load(a + m * lda + j, av);
+    VecIO<T, VEC>::load(b + m * ldb + j, bv);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) ov[v] = gelu_f(av[v]) * bv[v];
+    VecIO<T, VEC>::store(out + m * ldo + j, ov);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_mul_bwd_kernel(const T* __restrict__ dout, int64_t ldd, const T* __restrict__ a, int64_t lda,
+                    const T* __restrict__ b, int64_t ldb, T* __restrict__ da, int64_t ldda, T* __restrict__ db,
+                    int64_t lddb, int64_t M, int J) {
+  constexpr int VEC = 8;
+  const int nvec = J / VEC;
+  const int64_t total = M * nvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / nvec;
+    const int j = (int)(i % nvec) * VEC;
+    float gv[VEC], av[VEC], bv[VEC], dav[VEC], dbv[VEC];
+    VecIO<T, VEC>::load(dout + m * ldd + j, gv);
+    VecIO<T, VEC>::load(a + m * lda + j, av);
+    VecIO<T, VEC>::load(b + m * ldb + j, bv);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float g, dg;
+      gelu_and_grad(av[v], g, dg);
+      dav[v] = gv[v] * bv[v] * dg;
+      dbv[v] = gv[v] * g;
+    }
+    VecIO<T, VEC>::store(da + m * ldda + j, dav);
+    VecIO<T, VEC>::store(db + m * lddb + j, dbv);
+  }
+}
+
+// ---- RMSNorm: one warp per row, two passes over the row (the second hits L1/L2) ----------------
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+rms_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
+                    float* __restrict__ rstd, int64_t M, int H, float eps) {
+  constexpr int VEC = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t m = warp; m < M; m += nwarps) {
+    const TX* xr = x + m * H;
+    float ss = 0.f;
+    for (int j = lane * VEC; j < H; j += 32 * VEC) {
+      float v[VEC];
+      VecIO<TX, VEC>::load(xr + j, v);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) ss = fmaf(v[q], v[q], ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    if (lane == 0) rstd[m] = inv;
+    TY* yr = y + m * H;
+    for (int j = lane * VEC; j < H; j += 32 * VEC) {
+      float v[VEC], wv[VEC], o[VEC];
+      VecIO<TX, VEC>::load(xr + j, v);
+      VecIO<float, VEC>::load(w + j, wv);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) o[q] = (v[q] * inv) * wv[q];
+      VecIO<TY, VEC>::store(yr + j, o);
+    }
+  }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd;  dw partial = sum_rows dy * xhat
+// Each warp walks rows m = warp, warp + nwarps, ...; per-lane column accumulators for dw live in
+// registers (NCH chunks of 4 columns), are summed across the CTA's warps in shared memory in fixed
+// order, and written as one partial row per CTA.
+template <typename TX, typename TY, int NCH>
+__global__ void __launch_bounds__(256)
+rms_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                    const float* __restrict__ rstd, TX* __restrict__ dx, float* __restrict__ dw_partial, int64_t M,
+                    int H) {
+  constexpr int VEC = 4;
+  extern __shared__ float red[];  // [warps][H]
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int64_t warp = (int64_t)blockIdx.x * nw + wid;
+  const int64_t nwarps = (int64_t)gridDim.x * nw;
+  float acc[NCH][VEC];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[c][q] = 0.f;
+
+  for (int64_t m = warp; m < M; m += nwarps) {
+    const TX* xr = x + m * H;
+    const TY* gr = dy + m * H;
+    const float inv = rstd[m];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int j = (c * 32 + lane) * VEC;
+      if (j < H) {
+        float xv[VEC], gv[VEC], wv[VEC];
+        VecIO<TX, VEC>::load(xr + j, xv);
+        VecIO<TY, VEC>::load(gr + j, gv);
+        VecIO<float, VEC>::load(w + j, wv);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) dot = fmaf(gv[q] * wv[q], xv[q] * inv, dot);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float cmean = dot / (float)H;
+    TX* dr = dx + m * H;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int j = (c * 32 + lane) * VEC;
+      if (j < H) {
+        float xv[VEC], gv[VEC], wv[VEC], o[VEC];
+        VecIO<TX, VEC>::load(xr + j, xv);
+        VecIO<TY, VEC>::load(gr + j, gv);
+        VecIO<float, VEC>::load(w + j, wv);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) {
+          const float xh = xv[q] * inv;
+          o[q] = inv * (gv[q] * wv[q] - xh * cmean);
+          acc[c][q] = fmaf(gv[q], xh, acc[c][q]);
+        }
+        VecIO<TX, VEC>::store(dr + j, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int j = (c * 32 + lane) * VEC;
+    if (j < H) {
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) red[wid * H + j + q] = acc[c][q];
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < nw; ++k) s += red[k * H + j];
+    dw_partial[(int64_t)blockIdx.x * H + j] = s;
+  }
+}
+
+__global__ void rows_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int H) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= H) return;
+  float s = 0.f;
+  for (int r = 0; r < rows; ++r) s += partial[(int64_t)r * H + j];
+  out[j] = s;
+}
+
+constexpr int kNormBwdCtas = 296;  // two per SM
+constexpr int kNormBwdWarps = 8;
+
+static unsigned grid_for(int64_t work_items, int per_block) {
+  const int64_t want = (work_items + per_block - 1) / per_block;
+  const int64_t cap = 148LL * 16;
+  return (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+}  // namespace hawk
+
+using namespace hawk;
+using bf = __nv_bfloat16;
+
+extern "C" int hawk_gelu_mul_fwd(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo,
+                                 int64_t M, int J, int dtype, void* stream) {
+  HAWK_REQUIRE(a && b && out, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(M >= 1 && J >= 8 && J % 8 == 0 && lda >= J && ldb >= J && ldo >= J, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16) && lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0,
+               HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(M * (J / 8), 256);
+  if (dtype == HAWK_BF16)
+    gelu_mul_fwd_kernel<bf><<<grid, 256, 0, st>>>(static_cast<const bf*>(a), lda, static_cast<const bf*>(b), ldb,
+                                                  static_cast<bf*>(out), ldo, M, J);
+  else
+    gelu_mul_fwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(a), lda, static_cast<const float*>(b),
+                                                     ldb, static_cast<float*>(out), ldo, M, J);
+  return launch_status();
+}
+
+extern "C" int hawk_gelu_mul_bwd(const void* dout, int64_t ldd, const void* a, int64_t lda, const void* b, int64_t ldb,
+                                 void* da, int64_t ldda, void* db, int64_t lddb, int64_t M, int J, int dtype,
+                                 void* stream) {
+  HAWK_REQUIRE(dout && a && b && da && db, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(M >= 1 && J >= 8 && J % 8 == 0 && ldd >= J && lda >= J && ldb >= J && ldda >= J && lddb >= J,
+               HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(aligned(dout, 16) && aligned(a, 16) && aligned(b, 16) && aligned(da, 16) && aligned(db, 16) &&
+                   ldd % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldda % 8 == 0 && lddb % 8 == 0,
+               HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(M * (J / 8), 256);
+  if (dtype == HAWK_BF16)
+    gelu_mul_bwd_kernel<bf><<<grid, 256, 0, st>>>(static_cast<const bf*>(dout), ldd, static_cast<const bf*>(a), lda,
+                                                  static_cast<const bf*>(b), ldb, static_cast<bf*>(da), ldda,
+                                                  static_cast<bf*>(db), lddb, M, J);
+  else
+    gelu_mul_bwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(dout), ldd, static_cast<const float*>(a),
+                                                     lda, static_cast<const float*>(b), ldb, static_cast<float*>(da),
+                                                     ldda, static_cast<float*>(db), lddb, M, J);
+  return launch_status();
+}
+
+extern "C" int hawk_rms_norm_fwd(const void* x, const float* w, void* y, float* rstd, int64_t M, int H, float eps,
+                                 int x_dtype, int y_dtype, void* stream) {
+  HAWK_REQUIRE(x && w && y && rstd, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(x_dtype) && valid_dtype(y_dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(M >= 1 && H >= 4 && H % 4 == 0, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 16), HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = grid_for(M, 8);
+#define HAWK_NORM_FWD(TX, TY)                                                                         \
+  rms_norm_fwd_kernel<TX, TY><<<grid, 256, 0, st>>>(static_cast<const TX*>(x), w, static_cast<TY*>(y), rstd, M, H, eps)
+  if (x_dtype == HAWK_F32 && y_dtype == HAWK_BF16) HAWK_NORM_FWD(float, bf);
+  else if (x_dtype == HAWK_F32) HAWK_NORM_FWD(float, float);
+  else if (y_dtype == HAWK_BF16) HAWK_NORM_FWD(bf, bf);
+  else HAWK_NORM_FWD(bf, float);
+#undef HAWK_NORM_FWD
+  return launch_status();
+}
+
+extern "C" size_t hawk_rms_norm_bwd_workspace_bytes(int H) {
+  return H < 1 ? 0 : (size_t)kNormBwdCtas * (size_t)H * sizeof(float);
+}
+
+extern "C" int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
+                                 void* workspace, size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
+                                 void* stream) {
+  HAWK_REQUIRE(dy && x && w && rstd && dx && dw, HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(x_dtype) && valid_dtype(y_dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(M >= 1 && H >= 4 && H % 4 == 0 && H <= 4096, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(workspace && workspace_bytes >= hawk_rms_norm_bwd_workspace_bytes(H), HAWK_ERR_WORKSPACE);
+  HAWK_REQUIRE(aligned(dy, 16) && aligned(x, 16) && aligned(w, 16) && aligned(dx, 16) && aligned(workspace, 16),
+               HAWK_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  const int smem = kNormBwdWarps * H * (int)sizeof(float);
+  const int nch = (H + 127) / 128;
+#define HAWK_NORM_BWD_N(TX, TY, N)                                                                                  \
+  do {                                                                                                              \
+    auto kern = rms_norm_bwd_kernel<TX, TY, N>;                                                                     \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {             \
+      (void)cudaGetLastError();                                                                                     \
+      return HAWK_ERR_LAUNCH;                                                                                       \
+    }                                                                                                               \
+    kern<<<kNormBwdCtas, kNormBwdWarps * 32, smem, st>>>(static_cast<const TY*>(dy), static_cast<const TX*>(x), w,   \
+                                                         rstd, static_cast<TX*>(dx), partial, M, H);                \
+  } while (0)
+#define HAWK_NORM_BWD(TX, TY)                          \
+  do {                                                 \
+    if (nch <= 4) HAWK_NORM_BWD_N(TX, TY, 4);          \
+    else if (nch <= 16) HAWK_NORM_BWD_N(TX, TY, 16);   \
+    else HAWK_NORM_BWD_N(TX, TY, 32);                  \
+  } while (0)
+  if (x_dtype == HAWK_F32 && y_dtype == HAWK_BF16) HAWK_NORM_BWD(float, bf);
+  else if (x_dtype == HAWK_F32) HAWK_NORM_BWD(float, float);
+  else if (y_dtype == HAWK_BF16) HAWK_NORM_BWD(bf, bf);
+  else HAWK_NORM_BWD(bf, float);
+#undef HAWK_NORM_BWD
+#undef HAWK_NORM_BWD_N
+  int rc = launch_status();
+  if (rc != HAWK_OK) return rc;
+  rows_sum_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, kNormBwdCtas, H);
+  return launch_status();
+}

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhawk_b200.so")
@@ -31,6 +31,12 @@ SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_conv_step": (c_int, [_P, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_rglru_step": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "hawk_gelu_mul_fwd": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int, c_int, _P]),
+    "hawk_gelu_mul_bwd": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int,
+                                  c_int, _P]),
+    "hawk_rms_norm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
+    "hawk_rms_norm_bwd_workspace_bytes": (c_size_t, [c_int]),
+    "hawk_rms_norm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int, c_int, c_int, _P]),
     "hawk_linear_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "hawk_linear_ce_fwd_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }

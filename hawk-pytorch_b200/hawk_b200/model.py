@@ -63,9 +63,9 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x):
-        xf = x.float()
-        inv = torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
-        return (xf * inv).type_as(x) * self.weight
+        # under autocast the only consumer is a Linear, which would round its input to bf16 anyway
+        out_dtype = torch.bfloat16 if (x.is_cuda and torch.is_autocast_enabled("cuda")) else None
+        return ops.rms_norm(x, self.weight, self.eps, out_dtype=out_dtype)
 
 
 class BlockDiagonalLinear(nn.Module):
@@ -127,8 +127,7 @@ class MLP(nn.Module):
         nn.init.zeros_(self.resid_proj.weight)
 
     def forward(self, x):
-        gate, up = self.gate_up_proj(x).chunk(2, dim=-1)
-        return self.resid_proj(F.gelu(gate) * up)
+        return self.resid_proj(ops.geglu(self.gate_up_proj(x)))  # gelu(gate) * up in one pass
 
 
 class Hawk(nn.Module):
@@ -159,7 +158,7 @@ class Hawk(nn.Module):
         state = cache.recc_state[:, 0]
         h = ops.decode_rglru_step(xc, gx.to(xc.dtype), ga.to(xc.dtype), self.rg_lru_a_param.float(), state)
         cache.current_cache_size = 1
-        return self.resid_proj(F.gelu(y) * h[:, None])
+        return self.resid_proj(ops.gelu_mul(y, h[:, None]))
 
     def forward(self, x, layer_past: Optional[RNNCache] = None):
         cached = layer_past is not None and self.use_cache and layer_past.current_cache_size > 0
@@ -170,8 +169,8 @@ class Hawk(nn.Module):
 
         self.conv1d.out_dtype = xb.dtype  # store the conv result in the activation dtype
         xc = self.conv1d(xb)
-        gx = self.rg_lru_input_gate(xc)
-        ga = self.rg_lru_a_gate(xc)
+        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, self.rg_lru_input_gate.b,
+                                      self.rg_lru_a_gate.w, self.rg_lru_a_gate.b)
         h = ops.fused_linear_scan(xc, gx, ga, self.rg_lru_a_param.float())
         cache = None
         if self.use_cache:
@@ -183,7 +182,7 @@ class Hawk(nn.Module):
             layer_past.conv_state.copy_(tail)
             layer_past.update_cache(h[:, -1:])
             cache = layer_past
-        return self.resid_proj(F.gelu(y) * h), cache
+        return self.resid_proj(ops.gelu_mul(y, h)), cache
 
 
 class RNNLayer(nn.Module):

@@ -418,3 +418,256 @@ def fused_cross_entropy(lm_head_weight, act, labels):
     if act.dtype != lm_head_weight.dtype:
         act = act.to(lm_head_weight.dtype)
     return linear_ce(lm_head_weight, act, labels)[0]
+
+
+# ---------------------------------------------------------------------------------------------
+# glue around the GEMMs: gelu(a) * b and RMSNorm, one pass each
+# ---------------------------------------------------------------------------------------------
+def _as_rows(t: torch.Tensor):
+    """(tensor, M, pitch): t viewed as M rows of t.shape[-1] contiguous elements with one row pitch
+    (in elements), in place when its strides allow (e.g. a chunk of a projection output)."""
+    J = t.shape[-1]
+    M = t.numel() // J if J else 0
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0
+    if ok and t.dim() >= 2:
+        ld = t.stride(-2)
+        expect = ld
+        for d in range(t.dim() - 2, -1, -1):  # leading dims must collapse onto the row pitch
+            if t.shape[d] != 1 and t.stride(d) != expect:
+                ok = False
+                break
+            expect = t.stride(d) * t.shape[d]
+        ok = ok and ld % 8 == 0 and ld >= J
+    elif ok:
+        ld = J
+    if not ok:
+        t = t.contiguous()
+        ld = J
+    return t, M, ld
+
+
+@torch.library.custom_op("hawk_b200::gelu_mul_fwd", mutates_args=())
+def gelu_mul_fwd(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    lib = _lib.load()
+    av, M, lda = _as_rows(a)
+    bv, _, ldb = _as_rows(b)
+    out = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    with _on(a, "gelu_mul_fwd", 1):
+        _lib.check(lib.hawk_gelu_mul_fwd(av.data_ptr(), lda, bv.data_ptr(), ldb, out.data_ptr(), a.shape[-1], M,
+                                         a.shape[-1], _dt(a), _stream(a)), "hawk_gelu_mul_fwd")
+    return out
+
+
+@gelu_mul_fwd.register_fake
+def _(a, b):
+    return a.new_empty(a.shape)
+
+
+@torch.library.custom_op("hawk_b200::gelu_mul_bwd", mutates_args=())
+def gelu_mul_bwd(dout: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    J = a.shape[-1]
+    av, M, lda = _as_rows(a)
+    bv, _, ldb = _as_rows(b)
+    dv, _, ldd = _as_rows(dout)
+    da = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    db = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    with _on(a, "gelu_mul_bwd", 1):
+        _lib.check(lib.hawk_gelu_mul_bwd(dv.data_ptr(), ldd, av.data_ptr(), lda, bv.data_ptr(), ldb, da.data_ptr(), J,
+                                         db.data_ptr(), J, M, J, _dt(a), _stream(a)), "hawk_gelu_mul_bwd")
+    return da, db
+
+
+@gelu_mul_bwd.register_fake
+def _(dout, a, b):
+    return a.new_empty(a.shape), a.new_empty(a.shape)
+
+
+def _gm_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+
+
+def _gm_backward(ctx, dout):
+    a, b = ctx.saved_tensors
+    return gelu_mul_bwd(dout, a, b)
+
+
+gelu_mul_fwd.register_autograd(_gm_backward, setup_context=_gm_setup)
+
+
+def gelu_mul(a, b):
+    """gelu(a) * b (exact GELU) in one pass; a and b may be strided halves of a projection output."""
+    if b.dtype != a.dtype:
+        b = b.to(a.dtype)
+    return gelu_mul_fwd(a, b)
+
+
+@torch.library.custom_op("hawk_b200::geglu_fwd", mutates_args=())
+def geglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    """gelu(gu[..., :I]) * gu[..., I:] for a contiguous [.., 2I] projection output."""
+    lib = _lib.load()
+    gu = gu.contiguous()
+    I = gu.shape[-1] // 2
+    M = gu.numel() // (2 * I)
+    out = torch.empty(*gu.shape[:-1], I, dtype=gu.dtype, device=gu.device)
+    es = gu.element_size()
+    with _on(gu, "gelu_mul_fwd", 1):
+        _lib.check(lib.hawk_gelu_mul_fwd(gu.data_ptr(), 2 * I, gu.data_ptr() + I * es, 2 * I, out.data_ptr(), I, M, I,
+                                         _dt(gu), _stream(gu)), "hawk_gelu_mul_fwd")
+    return out
+
+
+@geglu_fwd.register_fake
+def _(gu):
+    return gu.new_empty(*gu.shape[:-1], gu.shape[-1] // 2)
+
+
+@torch.library.custom_op("hawk_b200::geglu_bwd", mutates_args=())
+def geglu_bwd(dout: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    """Gradient of geglu_fwd w.r.t. gu: both halves written straight into one [.., 2I] buffer."""
+    lib = _lib.load()
+    gu, dout = gu.contiguous(), dout.contiguous()
+    I = gu.shape[-1] // 2
+    M = gu.numel() // (2 * I)
+    dgu = torch.empty_like(gu)
+    es = gu.element_size()
+    with _on(gu, "gelu_mul_bwd", 1):
+        _lib.check(lib.hawk_gelu_mul_bwd(dout.data_ptr(), I, gu.data_ptr(), 2 * I, gu.data_ptr() + I * es, 2 * I,
+                                         dgu.data_ptr(), 2 * I, dgu.data_ptr() + I * es, 2 * I, M, I, _dt(gu),
+                                         _stream(gu)), "hawk_gelu_mul_bwd")
+    return dgu
+
+
+@geglu_bwd.register_fake
+def _(dout, gu):
+    return torch.empty_like(gu)
+
+
+geglu_fwd.register_autograd(lambda ctx, dout: geglu_bwd(dout, ctx.saved_tensors[0]),
+                            setup_context=lambda ctx, inputs, output: ctx.save_for_backward(inputs[0]))
+
+
+def geglu(gu):
+    """gelu(gate) * up for gu = [gate | up] (hawk/hawk.py:82-86)."""
+    return geglu_fwd(gu)
+
+
+@torch.library.custom_op("hawk_b200::rms_norm_fwd", mutates_args=())
+def rms_norm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    x, w = x.contiguous(), w.contiguous()
+    H = x.shape[-1]
+    M = x.numel() // H
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    with _on(x, "rms_norm_fwd", 1):
+        _lib.check(lib.hawk_rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), M, H, eps, _dt(x),
+                                         _DT[out_dtype], _stream(x)), "hawk_rms_norm_fwd")
+    return y, rstd
+
+
+@rms_norm_fwd.register_fake
+def _(x, w, eps, out_dtype):
+    return x.new_empty(x.shape, dtype=out_dtype), x.new_empty(x.numel() // x.shape[-1], dtype=torch.float32)
+
+
+@torch.library.custom_op("hawk_b200::rms_norm_bwd", mutates_args=())
+def rms_norm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    dy, x, w = dy.contiguous(), x.contiguous(), w.contiguous()
+    H = x.shape[-1]
+    M = x.numel() // H
+    dx = torch.empty_like(x)
+    dw = torch.empty(H, dtype=torch.float32, device=x.device)
+    ws_bytes = lib.hawk_rms_norm_bwd_workspace_bytes(H)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with _on(x, "rms_norm_bwd", 2):
+        _lib.check(lib.hawk_rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                         dw.data_ptr(), ws.data_ptr(), ws_bytes, M, H, _dt(x), _dt(dy), _stream(x)),
+                   "hawk_rms_norm_bwd")
+    return dx, dw
+
+
+@rms_norm_bwd.register_fake
+def _(dy, x, w, rstd):
+    return torch.empty_like(x), w.new_empty(w.shape, dtype=torch.float32)
+
+
+def _rn_setup(ctx, inputs, output):
+    x, w, _, _ = inputs
+    ctx.save_for_backward(x, w, output[1])
+    ctx.w_dtype = w.dtype
+
+
+def _rn_backward(ctx, dy, drstd):
+    x, w, rstd = ctx.saved_tensors
+    dx, dw = rms_norm_bwd(dy, x, w, rstd)
+    return dx, dw.to(ctx.w_dtype), None, None
+
+
+rms_norm_fwd.register_autograd(_rn_backward, setup_context=_rn_setup)
+
+
+def rms_norm(x, weight, eps: float = 1e-6, out_dtype=None):
+    """x * rsqrt(mean(x^2) + eps) * weight with fp32 statistics (hawk/hawk.py:47-58).  out_dtype=None
+    keeps x's dtype; under autocast the model asks for bf16, which is what the following Linear would
+    round its input to anyway."""
+    w32 = weight if weight.dtype == torch.float32 else weight.float()
+    return rms_norm_fwd(x, w32, eps, out_dtype or x.dtype)[0]
+
+
+# ---------------------------------------------------------------------------------------------
+# both block-diagonal gate projections of the recurrent block, without layout copies
+# ---------------------------------------------------------------------------------------------
+class _BlockDiagGates(torch.autograd.Function):
+    """gx = blockdiag(x; wx) + bx, ga = blockdiag(x; wa) + ba (hawk/external.py:224-233, called twice
+    at hawk/hawk.py:181-182).  The [M, nb*bw] activations are used as nb strided batches in place
+    (batch stride bw, row pitch nb*bw): cuBLAS strided-batch GEMMs read and write the final layout,
+    so no transposed copies are made in either direction."""
+
+    @staticmethod
+    def forward(ctx, x, wx, bx, wa, ba):
+        nb, bw, _ = wx.shape
+        R = nb * bw
+        shape = x.shape
+        x2 = x.reshape(-1, R)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        dt = x2.dtype
+        with torch.autocast("cuda", enabled=False):
+            xb = x2.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
+            out = torch.empty(2, M, R, dtype=dt, device=x.device)
+            wxc, wac = wx.to(dt), wa.to(dt)
+            torch.baddbmm(bx.to(dt).unsqueeze(1), xb, wxc, out=out[0].view(M, nb, bw).transpose(0, 1))
+            torch.baddbmm(ba.to(dt).unsqueeze(1), xb, wac, out=out[1].view(M, nb, bw).transpose(0, 1))
+        ctx.save_for_backward(x2, wxc, wac)
+        ctx.meta = (shape, nb, bw, wx.dtype, bx.dtype)
+        return out[0].view(shape), out[1].view(shape)
+
+    @staticmethod
+    def backward(ctx, dgx, dga):
+        x2, wxc, wac = ctx.saved_tensors
+        shape, nb, bw, wdt, bdt = ctx.meta
+        M, R = x2.shape
+        dt = x2.dtype
+        with torch.autocast("cuda", enabled=False):
+            dgx2 = dgx.reshape(M, R).to(dt).contiguous()
+            dga2 = dga.reshape(M, R).to(dt).contiguous()
+            gxb = dgx2.view(M, nb, bw).transpose(0, 1)
+            gab = dga2.view(M, nb, bw).transpose(0, 1)
+            xbT = x2.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
+            dwx = torch.bmm(xbT, gxb)
+            dwa = torch.bmm(xbT, gab)
+            dbx = dgx2.view(M, nb, bw).sum(dim=0, dtype=torch.float32)
+            dba = dga2.view(M, nb, bw).sum(dim=0, dtype=torch.float32)
+            dx = torch.empty(M, R, dtype=dt, device=x2.device)
+            dxb = dx.view(M, nb, bw).transpose(0, 1)
+            torch.bmm(gxb, wxc.transpose(1, 2), out=dxb)
+            torch.baddbmm(dxb, gab, wac.transpose(1, 2), out=dxb)
+        return dx.view(shape), dwx.to(wdt), dbx.to(bdt), dwa.to(wdt), dba.to(bdt)
+
+
+def block_diag_gates(x, wx, bx, wa, ba):
+    """(input-gate, recurrence-gate) pre-activations of the RG-LRU from the conv output x [..., R]."""
+    return _BlockDiagGates.apply(x, wx, bx, wa, ba)

@@ -141,6 +141,31 @@ int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const int64_t* l
                            float* dweight, float* dact, void* workspace, size_t workspace_bytes,
                            int64_t N, int64_t H, int64_t V, int dtype, int* status, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Glue of the block around the GEMMs, one HBM pass each (reference: eager torch ops).
+ *
+ * gelu_mul: out[m,j] = gelu(a[m,j]) * b[m,j], exact (erf) GELU.  Replaces `F.gelu(gate) * up`
+ *   (hawk/hawk.py:82-86) and `F.gelu(y) * h` (hawk/hawk.py:134-135).  a, b, out and the gradients are
+ *   [M,J] with unit column stride and their own row pitch in ELEMENTS, so the two halves of a
+ *   projection output are read in place and both gradients can land in the halves of one buffer.
+ *   J and every pitch multiples of 8; pointers 16-byte aligned; one `dtype` for all tensors.
+ * rms_norm: y = x * rsqrt(mean_j x^2 + eps) * w, statistics in fp32 (hawk/hawk.py:47-58); x, dx in
+ *   `x_dtype`, y, dy in `y_dtype` (bf16 y from fp32 x is what autocast makes of the next Linear's
+ *   input); w, dw, rstd [M] fp32.  H multiple of 4 (backward: H <= 4096).  Backward workspace:
+ *   hawk_rms_norm_bwd_workspace_bytes(H).
+ * ---------------------------------------------------------------------------------------- */
+int hawk_gelu_mul_fwd(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo,
+                      int64_t M, int J, int dtype, void* stream);
+int hawk_gelu_mul_bwd(const void* dout, int64_t ldd, const void* a, int64_t lda, const void* b, int64_t ldb,
+                      void* da, int64_t ldda, void* db, int64_t lddb, int64_t M, int J, int dtype,
+                      void* stream);
+int hawk_rms_norm_fwd(const void* x, const float* w, void* y, float* rstd, int64_t M, int H, float eps,
+                      int x_dtype, int y_dtype, void* stream);
+size_t hawk_rms_norm_bwd_workspace_bytes(int H);
+int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
+                      void* workspace, size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

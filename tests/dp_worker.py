@@ -19,6 +19,11 @@ def patch_ops():
     M.ops.fused_linear_scan = lambda x, gx, ga, lam, h0=None: omodel.scan(x, gx, ga, lam)
     M.ops.fused_cross_entropy = lambda w, a, l: F.cross_entropy(F.linear(a, w), l)
     M.ops.Conv1D.forward = lambda self, x: omodel.conv1d(x, self.w, self.b)
+    M.ops.rms_norm = lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w)
+    M.ops.geglu = lambda gu: F.gelu(gu.chunk(2, -1)[0]) * gu.chunk(2, -1)[1]
+    M.ops.gelu_mul = lambda a, b: F.gelu(a) * b
+    M.ops.block_diag_gates = lambda x, wx, bx, wa, ba: (omodel.block_diag_linear(x, wx, bx),
+                                                        omodel.block_diag_linear(x, wa, ba))
 
 
 def make_trainer(world):

@@ -1,0 +1,100 @@
+"""The fused glue kernels (gelu(a)*b, RMSNorm, block-diagonal gate pair) against plain PyTorch fp32
+statements of the same ops.  fp32 <= 1e-5, bf16 <= 2e-2, norm-wise."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import max_rel, rel_l2
+from oracle import model as omodel
+
+pytestmark = pytest.mark.gpu
+
+
+def _tol(dtype):
+    return 1e-5 if dtype == torch.float32 else 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,J", [(1, 8), (7, 64), (300, 1024), (4096, 6144)])
+def test_geglu_and_strided_gelu_mul(dtype, M, J):
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(M + J)
+    gu = (2 * torch.randn(M, 2 * J, generator=g)).to(dtype)
+    go = torch.randn(M, J, generator=g).to(dtype)
+    ref_in = gu.float().double().requires_grad_(True)
+    ref = F.gelu(ref_in[:, :J]) * ref_in[:, J:]
+    ref.backward(go.double())
+    # fused whole-buffer form
+    x = gu.cuda().requires_grad_(True)
+    out = ops.geglu(x)
+    out.backward(go.cuda())
+    assert rel_l2(out.float().cpu(), ref.detach()) <= _tol(dtype)
+    assert rel_l2(x.grad.float().cpu(), ref_in.grad) <= _tol(dtype)
+    assert max_rel(x.grad.float().cpu(), ref_in.grad) <= _tol(dtype)
+    # strided-view form: a is the second half of a buffer, b contiguous (as gelu(y) * h in the block)
+    buf = gu.cuda().requires_grad_(True)
+    b = go.cuda().clone().requires_grad_(True)
+    out2 = ops.gelu_mul(buf[:, J:], b)
+    out2.backward(torch.ones_like(out2))
+    r_a = gu[:, J:].double().requires_grad_(True)
+    r_b = go.double().requires_grad_(True)
+    (F.gelu(r_a) * r_b).sum().backward()
+    assert rel_l2(out2.float().cpu(), (F.gelu(r_a) * r_b).detach()) <= _tol(dtype)
+    assert rel_l2(buf.grad[:, J:].float().cpu(), r_a.grad) <= _tol(dtype)
+    assert float(buf.grad[:, :J].abs().max()) == 0.0
+    assert rel_l2(b.grad.float().cpu(), r_b.grad) <= _tol(dtype)
+
+
+@pytest.mark.parametrize("xdt,ydt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                     (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("M,H", [(1, 64), (33, 512), (1000, 2048), (257, 4096)])
+def test_rms_norm_matches_torch(xdt, ydt, M, H):
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(M + H)
+    x = (3 * torch.randn(M, H, generator=g)).to(xdt)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    go = torch.randn(M, H, generator=g).to(ydt)
+    xr = x.double().requires_grad_(True)
+    wr = w.double().requires_grad_(True)
+    ref = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    ref.backward(go.double())
+    xd = x.cuda().requires_grad_(True)
+    wd = w.cuda().requires_grad_(True)
+    y = ops.rms_norm(xd, wd, 1e-6, out_dtype=ydt)
+    assert y.dtype == ydt
+    y.backward(go.cuda())
+    assert rel_l2(y.float().cpu(), ref.detach()) <= _tol(ydt)
+    assert rel_l2(xd.grad.float().cpu(), xr.grad) <= _tol(xdt if xdt == ydt else ydt)
+    assert rel_l2(wd.grad.cpu(), wr.grad) <= (1e-5 if ydt == torch.float32 else 2e-2)
+    # determinism of the two-stage weight-gradient reduction
+    xd2 = x.cuda().requires_grad_(True)
+    wd2 = w.cuda().requires_grad_(True)
+    ops.rms_norm(xd2, wd2, 1e-6, out_dtype=ydt).backward(go.cuda())
+    assert torch.equal(wd.grad, wd2.grad) and torch.equal(xd.grad, xd2.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nb,bw,lead", [(4, 16, (2, 5)), (16, 32, (3, 100)), (16, 128, (2, 300))])
+def test_block_diag_gates_match_einsum(dtype, nb, bw, lead):
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(nb + bw)
+    R = nb * bw
+    x = torch.randn(*lead, R, generator=g).to(dtype)
+    ws = [torch.randn(nb, bw, bw, generator=g) / bw ** 0.5 for _ in range(2)]
+    bs = [0.1 * torch.randn(nb, bw, generator=g) for _ in range(2)]
+    gos = [torch.randn(*lead, R, generator=g).to(dtype) for _ in range(2)]
+    xr = x.double().requires_grad_(True)
+    pr = [t.double().requires_grad_(True) for t in (ws[0], bs[0], ws[1], bs[1])]
+    r1 = omodel.block_diag_linear(xr, pr[0], pr[1])
+    r2 = omodel.block_diag_linear(xr, pr[2], pr[3])
+    torch.autograd.backward([r1, r2], [gos[0].double(), gos[1].double()])
+    xd = x.cuda().requires_grad_(True)
+    pd = [t.cuda().requires_grad_(True) for t in (ws[0], bs[0], ws[1], bs[1])]
+    o1, o2 = ops.block_diag_gates(xd, *pd)
+    assert o1.is_contiguous() and o2.is_contiguous() and o1.dtype == dtype
+    torch.autograd.backward([o1, o2], [gos[0].cuda(), gos[1].cuda()])
+    tol = _tol(dtype) if dtype == torch.bfloat16 else 2e-3  # fp32 bmm may run as TF32 on tensor cores
+    assert rel_l2(o1.float().cpu(), r1.detach()) <= tol and rel_l2(o2.float().cpu(), r2.detach()) <= tol
+    assert rel_l2(xd.grad.float().cpu(), xr.grad) <= tol
+    for a, b in zip(pd, pr):
+        assert rel_l2(a.grad.cpu(), b.grad) <= tol
