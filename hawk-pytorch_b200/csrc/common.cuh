@@ -111,6 +111,65 @@ struct VecIO<__nv_bfloat16, 4> {
   }
 };
 
+template <>
+struct VecIO<float, 2> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[2]) {
+    const float2 a = __ldg(reinterpret_cast<const float2*>(p));
+    v[0] = a.x; v[1] = a.y;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[2]) {
+    *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+  }
+};
+template <>
+struct VecIO<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
+    const float2 a = unpack_bf16x2(__ldg(reinterpret_cast<const uint32_t*>(p)));
+    v[0] = a.x; v[1] = a.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[2]) {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(v[0], v[1]);
+  }
+};
+
+// ---- the same, kept packed between the load and its use (half the registers for bf16) --------
+template <typename T, int VEC>
+struct RawVec;
+template <>
+struct RawVec<__nv_bfloat16, 4> {
+  using type = uint2;
+  static __device__ __forceinline__ type load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
+  static __device__ __forceinline__ type zero() { return make_uint2(0u, 0u); }
+  static __device__ __forceinline__ void unpack(type r, float (&v)[4]) {
+    const float2 a = unpack_bf16x2(r.x), b = unpack_bf16x2(r.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+};
+template <>
+struct RawVec<__nv_bfloat16, 2> {
+  using type = uint32_t;
+  static __device__ __forceinline__ type load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+  static __device__ __forceinline__ type zero() { return 0u; }
+  static __device__ __forceinline__ void unpack(type r, float (&v)[2]) {
+    const float2 a = unpack_bf16x2(r);
+    v[0] = a.x; v[1] = a.y;
+  }
+};
+template <>
+struct RawVec<float, 4> {
+  using type = float4;
+  static __device__ __forceinline__ type load(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ type zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ void unpack(type r, float (&v)[4]) { v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w; }
+};
+template <>
+struct RawVec<float, 2> {
+  using type = float2;
+  static __device__ __forceinline__ type load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+  static __device__ __forceinline__ type zero() { return make_float2(0.f, 0.f); }
+  static __device__ __forceinline__ void unpack(type r, float (&v)[2]) { v[0] = r.x; v[1] = r.y; }
+};
+
 // ---- transcendental variants ---------------------------------------------------------------
 // FAST = one MUFU instruction each (bf16 storage hides their ~1e-7 error);
 // precise = the CUDA math library's fp32 functions (for fp32 storage, 1e-5 parity).

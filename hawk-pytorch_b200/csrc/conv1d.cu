@@ -15,14 +15,16 @@
 
 namespace hawk {
 
-constexpr int kConvFwdVec = 8;
-constexpr int kConvFwdRows = 32;  // time steps per thread
-constexpr int kConvBwdVec = 4;
-constexpr int kConvBwdRows = 32;
+// Few channels per thread keep the register footprint small (taps and windows are per channel), so
+// several CTAs share an SM and enough row loads are in flight to cover HBM latency.
+constexpr int kConvFwdVec = 4;
+constexpr int kConvFwdRows = 64;  // time steps per thread
+constexpr int kConvBwdVec = 2;
+constexpr int kConvBwdRows = 64;
 constexpr int kConvBwdTilesPerCta = 8;
 
 template <typename TI, typename TO, int W>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const float* __restrict__ w,
                   const float* __restrict__ bias, TO* __restrict__ y, int B, int T, int D, int n_ttiles) {
   constexpr int VEC = kConvFwdVec, TR = kConvFwdRows;
@@ -55,22 +57,24 @@ conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const floa
     }
   }
 
-  constexpr int U = 4;  // rows loaded together
+  constexpr int U = 8;  // rows loaded together
+#pragma unroll 1
   for (int tb = 0; tb < TR; tb += U) {
-    float cur[U][VEC];
+    typename RawVec<TI, VEC>::type raw[U];  // kept packed until used
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int t = t0 + tb + u;
-      if (t < T) VecIO<TI, VEC>::load(xp + (int64_t)t * xrs, cur[u]);
+      raw[u] = t < T ? RawVec<TI, VEC>::load(xp + (int64_t)t * xrs) : RawVec<TI, VEC>::zero();
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int t = t0 + tb + u;
       if (t >= T) break;
-      float out[VEC];
+      float cur[VEC], out[VEC];
+      RawVec<TI, VEC>::unpack(raw[u], cur);
 #pragma unroll
       for (int v = 0; v < VEC; ++v) {
-        float acc = wv[W - 1][v] * cur[u][v];
+        float acc = wv[W - 1][v] * cur[v];
 #pragma unroll
         for (int k = 1; k < W; ++k) acc = fmaf(wv[W - 1 - k][v], win[k - 1][v], acc);
         out[v] = acc + bv[v];
@@ -80,14 +84,14 @@ conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const floa
       for (int v = 0; v < VEC; ++v) {
 #pragma unroll
         for (int j = W - 2; j > 0; --j) win[j][v] = win[j - 1][v];
-        if (W > 1) win[0][v] = cur[u][v];
+        if (W > 1) win[0][v] = cur[v];
       }
     }
   }
 }
 
 template <typename TG, typename TX, int W>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t xbs, int64_t xrs,
                   const float* __restrict__ w, TX* __restrict__ dx, int64_t dxbs, int64_t dxrs,
                   float* __restrict__ partial, int T, int D, int n_ttiles) {
@@ -143,29 +147,28 @@ conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t x
       }
     }
 
-    constexpr int U = 4;
+    constexpr int U = 8;
+#pragma unroll 1
     for (int tb = 0; tb < TR; tb += U) {
-      float xin[U][VEC], gin[U][VEC];
+      typename RawVec<TX, VEC>::type xraw[U];  // kept packed until used
+      typename RawVec<TG, VEC>::type graw[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int t = t0 + tb + u;
-        if (t < T) VecIO<TX, VEC>::load(xp + (int64_t)t * xrs, xin[u]);
-        if (t + W - 1 < T) {
-          VecIO<TG, VEC>::load(gp + (int64_t)(t + W - 1) * D, gin[u]);
-        } else {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) gin[u][v] = 0.f;
-        }
+        xraw[u] = t < T ? RawVec<TX, VEC>::load(xp + (int64_t)t * xrs) : RawVec<TX, VEC>::zero();
+        graw[u] = t + W - 1 < T ? RawVec<TG, VEC>::load(gp + (int64_t)(t + W - 1) * D) : RawVec<TG, VEC>::zero();
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int t = t0 + tb + u;
         if (t >= T) break;
-        float out[VEC];
+        float out[VEC], xin[VEC], gin[VEC];
+        RawVec<TX, VEC>::unpack(xraw[u], xin);
+        RawVec<TG, VEC>::unpack(graw[u], gin);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
-          xw[0][v] = xin[u][v];
-          gw[W - 1][v] = gin[u][v];
+          xw[0][v] = xin[v];
+          gw[W - 1][v] = gin[v];
           float s = 0.f;
 #pragma unroll
           for (int k = 0; k < W; ++k) {

@@ -416,19 +416,60 @@ ce_loss_final_kernel(const float* __restrict__ partial, int n, float inv_n, floa
   if (threadIdx.x == 0) *loss = red[0] * inv_n;
 }
 
-// logits [N, ldl] bf16 -> dprobs = (exp(logit - lse) - onehot) / N, in place, and its transpose [V, ldt]
+// logits [N, ldl] bf16 -> dprobs = (exp(logit - lse) - onehot) / N, in place, and its transpose [V, ldt].
+// 64x64 tiles through shared memory; interior tiles move 16 bytes per thread in both directions.
 __global__ void __launch_bounds__(256)
 ce_dprobs_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, __nv_bfloat16* __restrict__ dpT, long long ldt,
                  const float* __restrict__ lse, const long long* __restrict__ labels, int N, int V, float inv_n) {
   __shared__ __nv_bfloat16 tile[64][66];
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const bool interior = r0 + 64 <= N && c0 + 64 <= V && (ldl % 8) == 0 && (ldt % 8) == 0;
+  if (interior) {
+    const int c8 = (threadIdx.x & 7) * 8;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int i = pass * 32 + (threadIdx.x >> 3);
+      const int r = r0 + i;
+      __nv_bfloat16* src = logits + (long long)r * ldl + c0 + c8;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src);
+      const float l = lse[r];
+      const int lab = (int)(labels[r] - (long long)(c0 + c8));  // 0..7 when the label is in this vector
+      const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t out[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack_bf16x2(in[q]);
+        float p0 = __expf(f.x - l), p1 = __expf(f.y - l);
+        if (lab == 2 * q) p0 -= 1.f;
+        if (lab == 2 * q + 1) p1 -= 1.f;
+        out[q] = pack_bf16x2(p0 * inv_n, p1 * inv_n);
+        *reinterpret_cast<uint32_t*>(&tile[i][c8 + 2 * q]) = out[q];
+      }
+      *reinterpret_cast<uint4*>(src) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+    __syncthreads();
+    const int r8 = (threadIdx.x & 7) * 8;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int c = pass * 32 + (threadIdx.x >> 3);
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t lo = *reinterpret_cast<const unsigned short*>(&tile[r8 + 2 * q][c]);
+        const uint32_t hi = *reinterpret_cast<const unsigned short*>(&tile[r8 + 2 * q + 1][c]);
+        o[q] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(dpT + (long long)(c0 + c) * ldt + r0 + r8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   for (int i = ty; i < 64; i += 4) {
     const int r = r0 + i, c = c0 + tx;
     __nv_bfloat16 v = __float2bfloat16(0.f);
     if (r < N && c < V) {
       const float lg = __bfloat162float(logits[(long long)r * ldl + c]);
-      float p = expf(lg - lse[r]);
+      float p = __expf(lg - lse[r]);
       if ((long long)c == labels[r]) p -= 1.f;
       v = __float2bfloat16(p * inv_n);
       logits[(long long)r * ldl + c] = v;

@@ -54,7 +54,7 @@ def test_conv_argument_validation_needs_no_gpu():
     assert lib.hawk_conv1d_fwd(p, 0, 64, p, p, p, 1, 8, 64, 5, 1, 1, None) == -7   # width 5 unsupported
     assert lib.hawk_conv1d_fwd(p, 0, 64, p, p, p, 1, 8, 60, 4, 1, 1, None) == -2   # D % 8
     assert lib.hawk_conv1d_fwd(p, 0, 68, p, p, p, 1, 8, 64, 4, 1, 1, None) == -4   # row stride % 8
-    assert lib.hawk_conv1d_bwd_workspace_bytes(8, 4096, 2048, 4) == 8 * 16 * 5 * 2048 * 4
+    assert lib.hawk_conv1d_bwd_workspace_bytes(8, 4096, 2048, 4) == 8 * 8 * 5 * 2048 * 4  # 64-row tiles, 8 per CTA
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
