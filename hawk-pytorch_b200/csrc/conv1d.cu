@@ -11,6 +11,8 @@
 //   dw[W-1-k,d] = sum_{b,t} go[b,t,d] x[b,t-k,d],   dbias[d] = sum_{b,t} go[b,t,d]
 // Parameter gradients: per-thread fp32 partials -> shared-memory sum over the CTA's time tiles
 // -> one partial row per CTA in the workspace -> fixed-order final reduction (deterministic).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace hawk {
@@ -58,18 +60,19 @@ conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const floa
   }
 
   constexpr int U = 8;  // rows loaded together
-#pragma unroll 1
-  for (int tb = 0; tb < TR; tb += U) {
+  // One batch of U rows.  FULL = the whole tile lies inside the sequence: no per-row predicates.
+  auto batch = [&](int tb, auto full_tag) {
+    constexpr bool FULL = decltype(full_tag)::value;
     typename RawVec<TI, VEC>::type raw[U];  // kept packed until used
+    const TI* xrow = xp + (int64_t)(t0 + tb) * xrs;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int t = t0 + tb + u;
-      raw[u] = t < T ? RawVec<TI, VEC>::load(xp + (int64_t)t * xrs) : RawVec<TI, VEC>::zero();
+      raw[u] = (FULL || t0 + tb + u < T) ? RawVec<TI, VEC>::load(xrow + (int64_t)u * xrs) : RawVec<TI, VEC>::zero();
     }
+    TO* yrow = yp + (int64_t)(t0 + tb) * D;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int t = t0 + tb + u;
-      if (t >= T) break;
+      if (!FULL && t0 + tb + u >= T) break;
       float cur[VEC], out[VEC];
       RawVec<TI, VEC>::unpack(raw[u], cur);
 #pragma unroll
@@ -79,7 +82,7 @@ conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const floa
         for (int k = 1; k < W; ++k) acc = fmaf(wv[W - 1 - k][v], win[k - 1][v], acc);
         out[v] = acc + bv[v];
       }
-      VecIO<TO, VEC>::store(yp + (int64_t)t * D, out);
+      VecIO<TO, VEC>::store(yrow + (int64_t)u * D, out);
 #pragma unroll
       for (int v = 0; v < VEC; ++v) {
 #pragma unroll
@@ -87,6 +90,13 @@ conv1d_fwd_kernel(const TI* __restrict__ x, int64_t xbs, int64_t xrs, const floa
         if (W > 1) win[0][v] = cur[v];
       }
     }
+  };
+  if (t0 + TR <= T) {
+#pragma unroll 1
+    for (int tb = 0; tb < TR; tb += U) batch(tb, std::true_type{});
+  } else {
+#pragma unroll 1
+    for (int tb = 0; tb < TR; tb += U) batch(tb, std::false_type{});
   }
 }
 
@@ -148,20 +158,23 @@ conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t x
     }
 
     constexpr int U = 8;
-#pragma unroll 1
-    for (int tb = 0; tb < TR; tb += U) {
+    // One batch of U rows.  FULL = rows t .. t+W-1 all lie inside the sequence: no predicates.
+    auto batch = [&](int tb, auto full_tag) {
+      constexpr bool FULL = decltype(full_tag)::value;
       typename RawVec<TX, VEC>::type xraw[U];  // kept packed until used
       typename RawVec<TG, VEC>::type graw[U];
+      const TX* xrow = xp + (int64_t)(t0 + tb) * xrs;
+      const TG* grow = gp + (int64_t)(t0 + tb + W - 1) * D;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int t = t0 + tb + u;
-        xraw[u] = t < T ? RawVec<TX, VEC>::load(xp + (int64_t)t * xrs) : RawVec<TX, VEC>::zero();
-        graw[u] = t + W - 1 < T ? RawVec<TG, VEC>::load(gp + (int64_t)(t + W - 1) * D) : RawVec<TG, VEC>::zero();
+        xraw[u] = (FULL || t < T) ? RawVec<TX, VEC>::load(xrow + (int64_t)u * xrs) : RawVec<TX, VEC>::zero();
+        graw[u] = (FULL || t + W - 1 < T) ? RawVec<TG, VEC>::load(grow + (int64_t)u * D) : RawVec<TG, VEC>::zero();
       }
+      TX* dxrow = dxp + (int64_t)(t0 + tb) * dxrs;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const int t = t0 + tb + u;
-        if (t >= T) break;
+        if (!FULL && t0 + tb + u >= T) break;
         float out[VEC], xin[VEC], gin[VEC];
         RawVec<TX, VEC>::unpack(xraw[u], xin);
         RawVec<TG, VEC>::unpack(graw[u], gin);
@@ -178,7 +191,7 @@ conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t x
           acc[W][v] += gw[0][v];  // dbias
           out[v] = s;
         }
-        VecIO<TX, VEC>::store(dxp + (int64_t)t * dxrs, out);
+        VecIO<TX, VEC>::store(dxrow + (int64_t)u * dxrs, out);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
 #pragma unroll
@@ -187,6 +200,13 @@ conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t x
           for (int j = 0; j < W - 1; ++j) gw[j][v] = gw[j + 1][v];
         }
       }
+    };
+    if (t0 + TR + W - 1 <= T) {
+#pragma unroll 1
+      for (int tb = 0; tb < TR; tb += U) batch(tb, std::true_type{});
+    } else {
+#pragma unroll 1
+      for (int tb = 0; tb < TR; tb += U) batch(tb, std::false_type{});
     }
   }
 
