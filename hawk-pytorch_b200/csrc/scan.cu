@@ -55,6 +55,15 @@ __device__ __forceinline__ float gate_scale(float lam) {
   return FAST ? kGateC * sp * kLog2e : kGateC * sp;
 }
 
+// ---- arithmetic on a lane's channel pair -------------------------------------------------------
+// sm_100 has packed fp32x2 add/mul/fma: one issue slot for both channels.  The kernels are issue
+// bound (about 40 instructions per element), so the FAST path does its FP32 work two at a time.
+__device__ __forceinline__ float2 f2(float v) { return make_float2(v, v); }
+__device__ __forceinline__ float2 neg2(float2 v) { return make_float2(-v.x, -v.y); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
 // i = sigmoid(gx) and r = sigmoid(ga).  FAST shares one reciprocal between the two:
 // 1/(1+eg) = (1+ea) / ((1+eg)(1+ea)), three MUFU operations instead of four.  The exponent is
 // capped so that the product stays finite (sigmoid(-30) is 9e-14 already).
@@ -72,18 +81,64 @@ __device__ __forceinline__ void sigmoid_pair(float gx, float ga, float& i, float
   }
 }
 
+// both gates of both channels
+template <bool FAST>
+__device__ __forceinline__ void gates2(float2 gx, float2 ga, float2& i, float2& r) {
+  if (FAST) {
+    float2 tx = mul2(gx, f2(-kLog2e)), ta = mul2(ga, f2(-kLog2e));
+    tx.x = ex2_approx(fminf(tx.x, 43.f));
+    tx.y = ex2_approx(fminf(tx.y, 43.f));
+    ta.x = ex2_approx(fminf(ta.x, 43.f));
+    ta.y = ex2_approx(fminf(ta.y, 43.f));
+    const float2 u = add2(tx, f2(1.f)), v = add2(ta, f2(1.f));
+    float2 w = mul2(u, v);
+    w.x = rcp_approx(w.x);
+    w.y = rcp_approx(w.y);
+    i = mul2(v, w);
+    r = mul2(u, w);
+  } else {
+    sigmoid_pair<false>(gx.x, ga.x, i.x, r.x);
+    sigmoid_pair<false>(gx.y, ga.y, i.y, r.y);
+  }
+}
+
+// a = exp(k r) for both channels (k already in log2 units on the FAST path).
+// (Moving this exponential onto the FMA pipe as a polynomial was measured: same kernel time.)
+template <bool FAST>
+__device__ __forceinline__ float2 decay2(float2 k, float2 r) {
+  if (FAST) {
+    float2 t = mul2(k, r);
+    t.x = ex2_approx(t.x);
+    t.y = ex2_approx(t.y);
+    return t;
+  }
+  return make_float2(expf(k.x * r.x), expf(k.y * r.y));
+}
+
 template <bool FAST>
 __device__ __forceinline__ void fwd_coeffs(float x, float gx, float ga, float k, float& a, float& beta) {
   float i, r;
   sigmoid_pair<FAST>(gx, ga, i, r);
+  const float la = k * r;  // scan_fused.py:96
+  a = expf(la);
+  beta = (x * i) * sqrtf(1.f - expf(2.f * la));  // :99-105
+}
+
+// (a, beta) of one row for the lane's channel pair
+template <bool FAST>
+__device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, float2 k, float2& a, float2& beta) {
   if (FAST) {
-    a = ex2_approx(k * r);
-    const float v = fmaf(-a, a, 1.f);
-    beta = x * i * (v * rsqrt_approx(fmaxf(v, 1e-30f)));  // sqrt(v) with one MUFU operation
+    float2 i, r;
+    gates2<true>(gx, ga, i, r);
+    a = decay2<true>(k, r);
+    const float2 v = fma2(neg2(a), a, f2(1.f));
+    float2 rs;
+    rs.x = rsqrt_approx(fmaxf(v.x, 1e-30f));  // sqrt(v) = v * rsqrt(v), one MUFU operation
+    rs.y = rsqrt_approx(fmaxf(v.y, 1e-30f));
+    beta = mul2(mul2(x, i), mul2(v, rs));
   } else {
-    const float la = k * r;  // scan_fused.py:96
-    a = expf(la);
-    beta = (x * i) * sqrtf(1.f - expf(2.f * la));  // :99-105
+    fwd_coeffs<false>(x.x, gx.x, ga.x, k.x, a.x, beta.x);
+    fwd_coeffs<false>(x.y, gx.y, ga.y, k.y, a.y, beta.y);
   }
 }
 
@@ -91,26 +146,25 @@ __device__ __forceinline__ void fwd_coeffs(float x, float gx, float ga, float k,
 // warp (slot = lane / LPR, earlier slots first), by warp shuffles.  Composition of "earlier then
 // later" is (P_l * P_e, P_l * h_e + h_l).
 template <int NSUB, int LPR>
-__device__ __forceinline__ void slot_prefix(int sub, float& iP0, float& iP1, float& ih0, float& ih1, float& eP0,
-                                            float& eP1, float& eh0, float& eh1) {
-  eP0 = eP1 = 1.f;
-  eh0 = eh1 = 0.f;
+__device__ __forceinline__ void slot_prefix(int sub, float2& iP, float2& ih, float2& eP, float2& eh) {
+  eP = f2(1.f);
+  eh = f2(0.f);
   if (NSUB == 1) return;
+  constexpr unsigned kAll = 0xffffffffu;
 #pragma unroll
   for (int d = 1; d < NSUB; d <<= 1) {
-    const float qP0 = __shfl_up_sync(0xffffffffu, iP0, d * LPR), qP1 = __shfl_up_sync(0xffffffffu, iP1, d * LPR);
-    const float qh0 = __shfl_up_sync(0xffffffffu, ih0, d * LPR), qh1 = __shfl_up_sync(0xffffffffu, ih1, d * LPR);
+    const float2 qP = make_float2(__shfl_up_sync(kAll, iP.x, d * LPR), __shfl_up_sync(kAll, iP.y, d * LPR));
+    const float2 qh = make_float2(__shfl_up_sync(kAll, ih.x, d * LPR), __shfl_up_sync(kAll, ih.y, d * LPR));
     if (sub >= d) {
-      ih0 = fmaf(iP0, qh0, ih0);
-      ih1 = fmaf(iP1, qh1, ih1);
-      iP0 *= qP0;
-      iP1 *= qP1;
+      ih = fma2(iP, qh, ih);
+      iP = mul2(iP, qP);
     }
   }
-  const float qP0 = __shfl_up_sync(0xffffffffu, iP0, LPR), qP1 = __shfl_up_sync(0xffffffffu, iP1, LPR);
-  const float qh0 = __shfl_up_sync(0xffffffffu, ih0, LPR), qh1 = __shfl_up_sync(0xffffffffu, ih1, LPR);
+  const float2 qP = make_float2(__shfl_up_sync(kAll, iP.x, LPR), __shfl_up_sync(kAll, iP.y, LPR));
+  const float2 qh = make_float2(__shfl_up_sync(kAll, ih.x, LPR), __shfl_up_sync(kAll, ih.y, LPR));
   if (sub > 0) {
-    eP0 = qP0; eP1 = qP1; eh0 = qh0; eh1 = qh1;
+    eP = qP;
+    eh = qh;
   }
 }
 
@@ -140,7 +194,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
                 const float* __restrict__ lam, const float* __restrict__ h0, T* __restrict__ h,
                 int T_len, int D) {
   using G = Geo<T, R, WARPS, LPR, 3>;
-  using P = Pair<T>;
+  using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float4 carry[2][WARPS][LPR];     // (P.x, P.y, hl.x, hl.y) of each warp's rows
   __shared__ float2 state[2][LPR];            // CTA running state entering a super-step
@@ -157,7 +211,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   const size_t base = (size_t)b * T_len * D;
 
   const float2 lam2 = *reinterpret_cast<const float2*>(lam + ch);
-  const float k0 = gate_scale<FAST>(lam2.x), k1 = gate_scale<FAST>(lam2.y);
+  const float2 k2 = make_float2(gate_scale<FAST>(lam2.x), gate_scale<FAST>(lam2.y));
   if (threadIdx.x < LPR) {
     state[0][threadIdx.x] =
         h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch0 + 2 * threadIdx.x) : make_float2(0.f, 0.f);
@@ -218,51 +272,41 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     const int t0 = s * G::ROWS + slot * R;
 
     // phase 1: coefficients and chunk summary
-    float a[R][2], be[R][2];
-    float P0 = 1.f, P1 = 1.f, hl0 = 0.f, hl1 = 0.f;
+    float2 a[R], be[R];
+    float2 P = f2(1.f), hl = f2(0.f);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (FULL || t0 + r < T_len) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
-        const float2 xv = SmemPair<T>::ld(row);
-        const float2 gxv = SmemPair<T>::ld(row + G::IN_BYTES);
-        const float2 gav = SmemPair<T>::ld(row + 2 * G::IN_BYTES);
-        fwd_coeffs<FAST>(xv.x, gxv.x, gav.x, k0, a[r][0], be[r][0]);
-        fwd_coeffs<FAST>(xv.y, gxv.y, gav.y, k1, a[r][1], be[r][1]);
+        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld(row + G::IN_BYTES),
+                          SmemPair<T>::ld(row + 2 * G::IN_BYTES), k2, a[r], be[r]);
       } else {  // past the end: identity step
-        a[r][0] = a[r][1] = 1.f;
-        be[r][0] = be[r][1] = 0.f;
+        a[r] = f2(1.f);
+        be[r] = f2(0.f);
       }
-      hl0 = fmaf(a[r][0], hl0, be[r][0]);
-      hl1 = fmaf(a[r][1], hl1, be[r][1]);
-      P0 *= a[r][0];
-      P1 *= a[r][1];
+      hl = fma2(a[r], hl, be[r]);
+      P = mul2(P, a[r]);
     }
     // phase 2: inbound state of this slot's chunk = (slots before it in the warp) o (warps before
     // it in the CTA) o (CTA running state)
-    float eP0, eP1, eh0, eh1;
-    slot_prefix<G::NSUB, LPR>(sub, P0, P1, hl0, hl1, eP0, eP1, eh0, eh1);  // P/hl become inclusive
-    if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P0, P1, hl0, hl1);
+    float2 eP, eh;
+    slot_prefix<G::NSUB, LPR>(sub, P, hl, eP, eh);  // P/hl become inclusive
+    if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P.x, P.y, hl.x, hl.y);
     __syncthreads();
     float2 hin = state[s & 1][cl];
     for (int j = 0; j < warp; ++j) {
       const float4 c = carry[s & 1][j][cl];
-      hin.x = fmaf(c.x, hin.x, c.z);
-      hin.y = fmaf(c.y, hin.y, c.w);
+      hin = fma2(make_float2(c.x, c.y), hin, make_float2(c.z, c.w));
     }
-    if (slot == G::SLOTS - 1) {
-      state[(s + 1) & 1][cl] = make_float2(fmaf(P0, hin.x, hl0), fmaf(P1, hin.y, hl1));
-    }
-    hin.x = fmaf(eP0, hin.x, eh0);
-    hin.y = fmaf(eP1, hin.y, eh1);
+    if (slot == G::SLOTS - 1) state[(s + 1) & 1][cl] = fma2(P, hin, hl);
+    hin = fma2(eP, hin, eh);
 
     // phase 3: replay from the true inbound state and store
     const uint32_t o0 = (uint32_t)t0 * uD;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      hin.x = fmaf(a[r][0], hin.x, be[r][0]);
-      hin.y = fmaf(a[r][1], hin.y, be[r][1]);
-      if (FULL || t0 + r < T_len) P::store(hp + (o0 + (uint32_t)r * uD), hin.x, hin.y);
+      hin = fma2(a[r], hin, be[r]);
+      if (FULL || t0 + r < T_len) P_::store(hp + (o0 + (uint32_t)r * uD), hin.x, hin.y);
     }
   };
 
@@ -281,7 +325,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
                 const T* __restrict__ go, T* __restrict__ dx, T* __restrict__ dgx, T* __restrict__ dga,
                 float* __restrict__ dlam_partial, float* __restrict__ dh0, int T_len, int D) {
   using G = Geo<T, R, WARPS, LPR, 5>;
-  using P = Pair<T>;
+  using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float4 carry[2][WARPS][LPR];
   __shared__ float2 state[2][LPR];
@@ -299,9 +343,9 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   const size_t base = (size_t)b * T_len * D;
 
   const float2 lam2 = *reinterpret_cast<const float2*>(lam + ch);
-  const float k0 = gate_scale<FAST>(lam2.x), k1 = gate_scale<FAST>(lam2.y);
+  const float2 k2 = make_float2(gate_scale<FAST>(lam2.x), gate_scale<FAST>(lam2.y));
   // factor that turns d(log a) into d(ga)/(r(1-r)):  C * softplus(lam), in natural-log units
-  const float q0 = FAST ? k0 * (1.f / kLog2e) : k0, q1 = FAST ? k1 * (1.f / kLog2e) : k1;
+  const float2 q2 = FAST ? make_float2(k2.x * (1.f / kLog2e), k2.y * (1.f / kLog2e)) : k2;
   const float2 h0v = h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch) : make_float2(0.f, 0.f);
   if (threadIdx.x < LPR) state[0][threadIdx.x] = make_float2(0.f, 0.f);  // c_T = 0
 
@@ -346,7 +390,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
-  float acc0 = 0.f, acc1 = 0.f;  // sum over t of dlog_a * r  (times C*sigmoid(lam) at the end)
+  float2 acc = f2(0.f);  // sum over t of dlog_a * r  (times C*sigmoid(lam) at the end)
   T* dxp = dx + base + ch;
   T* dgxp = dgx + base + ch;
   T* dgap = dga + base + ch;
@@ -364,46 +408,36 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     const int tt = T_len - 1 - (s * G::ROWS + slot * R);  // time of this slot's first (latest) row
 
     // phase 1: a_t, both gates and the chunk summary of c <- a * (go + c)
-    float a[R][2], rg[R][2], ig[R][2];
-    float P0 = 1.f, P1 = 1.f, cl0 = 0.f, cl1 = 0.f;
+    float2 a[R], rg[R], ig[R];
+    float2 P = f2(1.f), cloc = f2(0.f);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      float2 gov = make_float2(0.f, 0.f);
+      float2 gov = f2(0.f);
       if (FULL || tt - r >= 0) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
-        const float2 gav = SmemPair<T>::ld(row);
-        const float2 gxv = SmemPair<T>::ld(row + 3 * G::IN_BYTES);
         gov = SmemPair<T>::ld(row + G::IN_BYTES);
-        sigmoid_pair<FAST>(gxv.x, gav.x, ig[r][0], rg[r][0]);
-        sigmoid_pair<FAST>(gxv.y, gav.y, ig[r][1], rg[r][1]);
-        a[r][0] = FAST ? ex2_approx(k0 * rg[r][0]) : expf(k0 * rg[r][0]);
-        a[r][1] = FAST ? ex2_approx(k1 * rg[r][1]) : expf(k1 * rg[r][1]);
+        gates2<FAST>(SmemPair<T>::ld(row + 3 * G::IN_BYTES), SmemPair<T>::ld(row), ig[r], rg[r]);
+        a[r] = decay2<FAST>(k2, rg[r]);
       } else {
-        rg[r][0] = rg[r][1] = ig[r][0] = ig[r][1] = 0.f;
-        a[r][0] = a[r][1] = 1.f;
+        rg[r] = ig[r] = f2(0.f);
+        a[r] = f2(1.f);
       }
-      cl0 = a[r][0] * (gov.x + cl0);
-      cl1 = a[r][1] * (gov.y + cl1);
-      P0 *= a[r][0];
-      P1 *= a[r][1];
+      cloc = mul2(a[r], add2(gov, cloc));
+      P = mul2(P, a[r]);
     }
 
     // phase 2
-    float eP0, eP1, eh0, eh1;
-    slot_prefix<G::NSUB, LPR>(sub, P0, P1, cl0, cl1, eP0, eP1, eh0, eh1);
-    if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P0, P1, cl0, cl1);
+    float2 eP, eh;
+    slot_prefix<G::NSUB, LPR>(sub, P, cloc, eP, eh);
+    if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P.x, P.y, cloc.x, cloc.y);
     __syncthreads();
     float2 c = state[s & 1][cl];
     for (int j = 0; j < warp; ++j) {
       const float4 cj = carry[s & 1][j][cl];
-      c.x = fmaf(cj.x, c.x, cj.z);
-      c.y = fmaf(cj.y, c.y, cj.w);
+      c = fma2(make_float2(cj.x, cj.y), c, make_float2(cj.z, cj.w));
     }
-    if (slot == G::SLOTS - 1) {
-      state[(s + 1) & 1][cl] = make_float2(fmaf(P0, c.x, cl0), fmaf(P1, c.y, cl1));
-    }
-    c.x = fmaf(eP0, c.x, eh0);
-    c.y = fmaf(eP1, c.y, eh1);
+    if (slot == G::SLOTS - 1) state[(s + 1) & 1][cl] = fma2(P, c, cloc);
+    c = fma2(eP, c, eh);
 
     // phase 3: dh_t and everything that is linear in it
 #pragma unroll
@@ -414,43 +448,55 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       const float2 gov = SmemPair<T>::ld(row + G::IN_BYTES);
       const float2 xv = SmemPair<T>::ld(row + 2 * G::IN_BYTES);
       const float2 hpv = (FULL || t > 0) ? SmemPair<T>::ld(row + 4 * G::IN_BYTES) : h0v;
-      float o_dx[2], o_dgx[2], o_dga[2];
+      const float2 av = a[r], rv = rg[r], iv = ig[r];
+      const float2 dh = add2(gov, c);
+      c = mul2(av, dh);
+      float2 o_dx, o_dgx, o_dga;
+      if (FAST) {
+        // below the clamp (1 - a^2 < 2.5e-7, i.e. a within 1.3e-7 of 1) m = v * 2000 stands in
+        // for sqrt(v): both are < 5e-4 there, which bf16 storage cannot resolve against dh
+        const float2 a2 = mul2(av, av);
+        const float2 v = add2(f2(1.f), neg2(a2));
+        float2 rs;
+        rs.x = rsqrt_approx(fmaxf(v.x, 2.5e-7f));
+        rs.y = rsqrt_approx(fmaxf(v.y, 2.5e-7f));
+        const float2 m = mul2(v, rs);
+        const float2 xi = mul2(iv, xv);
+        const float2 dm = mul2(dh, m);
+        // dlog_a = dh * (h_{t-1} a + (i x) * (0.5 rs) * (-2 a^2))         scan_fused.py:10-15,221,244-252
+        const float2 dla = mul2(dh, fma2(mul2(xi, rs), neg2(a2), mul2(hpv, av)));
+        o_dx = mul2(dm, iv);                                       // :240
+        o_dgx = mul2(mul2(dm, xi), add2(f2(1.f), neg2(iv)));       // :242
+        o_dga = mul2(mul2(mul2(rv, add2(f2(1.f), neg2(rv))), dla), q2);  // :254
+        acc = fma2(dla, rv, acc);
+      } else {
+        float* pc = &c.x;  // silence unused warnings in this branch
+        (void)pc;
+        float dxs[2], dgxs[2], dgas[2];
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float go_e = e ? gov.y : gov.x;
-        const float x_e = e ? xv.y : xv.x;
-        const float hp_e = e ? hpv.y : hpv.x;
-        const float a_e = a[r][e], r_e = rg[r][e], i_e = ig[r][e];
-        float& c_e = e ? c.y : c.x;
-        const float dh = go_e + c_e;
-        c_e = a_e * dh;
-        float a2, m, sg;
-        if (FAST) {
-          // below the clamp (1 - a^2 < 2.5e-7, i.e. a within 1.3e-7 of 1) m = v * 2000 stands in
-          // for sqrt(v): both are < 5e-4 there, which bf16 storage cannot resolve against dh
-          a2 = a_e * a_e;
-          const float v = fmaf(-a_e, a_e, 1.f);
-          const float rs = rsqrt_approx(fmaxf(v, 2.5e-7f));
-          sg = 0.5f * rs;  // clipped_sqrt_grad, scan_fused.py:10-15
-          m = v * rs;
-        } else {
-          a2 = expf(2.f * ((e ? k1 : k0) * r_e));
+        for (int e = 0; e < 2; ++e) {
+          const float x_e = e ? xv.y : xv.x, hp_e = e ? hpv.y : hpv.x, dh_e = e ? dh.y : dh.x;
+          const float a_e = e ? av.y : av.x, r_e = e ? rv.y : rv.x, i_e = e ? iv.y : iv.x;
+          const float a2 = expf(2.f * ((e ? k2.y : k2.x) * r_e));
           const float v = 1.f - a2;
-          m = sqrtf(v);
-          sg = 1.f / sqrtf(fmaxf(4.f * v, 1e-6f));
+          const float m = sqrtf(v);
+          const float sg = 1.f / sqrtf(fmaxf(4.f * v, 1e-6f));
+          const float xi = i_e * x_e;
+          const float dm = dh_e * m;
+          const float dla = dh_e * (hp_e * a_e + xi * sg * (-2.f * a2));
+          dxs[e] = dm * i_e;
+          dgxs[e] = dm * xi * (1.f - i_e);
+          dgas[e] = (r_e * (1.f - r_e)) * dla * (e ? q2.y : q2.x);
+          if (e) acc.y = fmaf(dla, r_e, acc.y); else acc.x = fmaf(dla, r_e, acc.x);
         }
-        const float xi = i_e * x_e;
-        const float dm = dh * m;
-        const float dla = dh * (hp_e * a_e + xi * sg * (-2.f * a2));  // :221,244-252
-        o_dx[e] = dm * i_e;                                           // :240
-        o_dgx[e] = dm * xi * (1.f - i_e);                             // :242
-        o_dga[e] = (r_e * (1.f - r_e)) * dla * (e ? q1 : q0);         // :254
-        if (e) acc1 = fmaf(dla, r_e, acc1); else acc0 = fmaf(dla, r_e, acc0);
+        o_dx = make_float2(dxs[0], dxs[1]);
+        o_dgx = make_float2(dgxs[0], dgxs[1]);
+        o_dga = make_float2(dgas[0], dgas[1]);
       }
       const uint32_t o = (uint32_t)t * uD;
-      P::store(dxp + o, o_dx[0], o_dx[1]);
-      P::store(dgxp + o, o_dgx[0], o_dgx[1]);
-      P::store(dgap + o, o_dga[0], o_dga[1]);
+      P_::store(dxp + o, o_dx.x, o_dx.y);
+      P_::store(dgxp + o, o_dgx.x, o_dgx.y);
+      P_::store(dgap + o, o_dga.x, o_dga.y);
     }
   };
 
@@ -461,7 +507,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   cp_async_wait<0>();
 
   // d(lam) partial for this (batch row, channel pair): C * sigmoid(lam) * sum_t dlog_a * r
-  red[slot][cl] = make_float2(acc0, acc1);
+  red[slot][cl] = acc;
   __syncthreads();
   if (threadIdx.x < LPR) {
     const int c2 = threadIdx.x;
