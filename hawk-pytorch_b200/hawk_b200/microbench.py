@@ -4,6 +4,7 @@
     python -m hawk_b200.microbench conv1d    [--B 8 --T 4096 --D 2048 --dtype bf16]
     python -m hawk_b200.microbench linear_ce [--N 32760 --H 2048 --V 32000]
     python -m hawk_b200.microbench decode    [--B 256 --D 2048 --layers 24]
+    python -m hawk_b200.microbench decode_model [--B 256]   # one cached token of the 1.35 B model, eager vs CUDA graph
 
 Prints one JSON line per kernel with the achieved rate against its algorithmic work:
 scan 8 (forward) / 16 (backward) bytes per element in bf16, conv1d 4 / 6, linear_ce 6*N*H*V flop,
@@ -51,7 +52,7 @@ def _emit(name, ms, work, unit, **extra):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "decode"])
+    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "decode", "decode_model"])
     ap.add_argument("--B", type=int, default=None)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--D", type=int, default=2048)
@@ -65,7 +66,7 @@ def main(argv=None):
     ap.add_argument("--flush", action="store_true")
     a = ap.parse_args(argv)
     if a.B is None:
-        a.B = 256 if a.op == "decode" else 8
+        a.B = 256 if a.op.startswith("decode") else 8
     dev = torch.device("cuda")
     dt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
     es = 2 if a.dtype == "bf16" else 4
@@ -100,6 +101,24 @@ def main(argv=None):
         t = _time(lambda: ops.linear_ce(w, act, lab), max(3, a.iters // 4), 2, flush)
         ops.check_device_status()
         _emit("linear_ce", t, 6 * a.N * a.H * a.V, "TFLOP/s", N=a.N, H=a.H, V=a.V)
+    elif a.op == "decode_model":
+        from .generate import GraphedDecoder
+        from .model import HawkModel, hawk_1b_config
+        cfg = hawk_1b_config()
+        torch.manual_seed(0)
+        with torch.device(dev):
+            model = HawkModel(cfg, use_cache=True)
+        model = model.bfloat16()  # serving precision: weights are read once per token, 2 bytes each
+        prompt = torch.randint(1, cfg.vocab_size, (a.B, 16), generator=g, device=dev)
+        tok = torch.randint(1, cfg.vocab_size, (a.B, 1), generator=g, device=dev)
+        n_params = sum(p.numel() for p in model.parameters())
+        for use_graph in (False, True):
+            dec = GraphedDecoder(model, a.B, autocast=False, use_graph=use_graph)
+            dec.prefill(prompt)
+            ms = _time(lambda: dec.step(tok), a.iters, a.warmup)
+            print(json.dumps({"kernel": "decode_step_1.35B" + ("_cuda_graph" if use_graph else "_eager"),
+                              "ms": round(ms, 4), "tokens_per_s": round(a.B / (ms * 1e-3)),
+                              "weight_GBps": round(2 * n_params / (ms * 1e-3) / 1e9, 1), "B": a.B}), flush=True)
     else:
         x, gx, ga = (torch.randn(a.B, a.D, generator=g, device=dev).to(dt) for _ in range(3))
         xy = torch.randn(a.B, 2 * a.D, generator=g, device=dev).to(dt)

@@ -180,3 +180,33 @@ def test_torch_compile_runs_the_custom_ops():
             pytest.skip(f"inductor toolchain unavailable: {type(e).__name__}")
         raise
     assert abs(float(loss) - float(g["loss_dezero"])) <= TOL * float(g["loss_dezero"])
+
+
+@pytest.mark.parametrize("bf16_weights", [False, True])
+def test_graphed_decode_equals_eager_decode(bf16_weights):
+    """The CUDA-graph replay of the decode step gives the eager step's logits and cache contents."""
+    import hawk_b200.model as M
+    from hawk_b200.generate import GraphedDecoder
+    torch.manual_seed(2)
+    cfg = M.HawkConfig(300, 128, 256, 3, 128, 16, 4)
+    model = M.HawkModel(cfg, use_cache=True)
+    model.load_state_dict(omodel.dezero(dict(model.state_dict()), seed=4))
+    model = model.cuda()
+    if bf16_weights:
+        model = model.bfloat16()
+    ids = torch.randint(1, 300, (32, 12), device="cuda")
+    outs = []
+    for use_graph in (False, True):
+        dec = GraphedDecoder(model, 32, cache_dtype=torch.float32, autocast=not bf16_weights, use_graph=use_graph)
+        dec.prefill(ids[:, :7])
+        steps = [dec.step(ids[:, t:t + 1]).float().clone() for t in range(7, 12)]
+        outs.append((steps, dec.caches[1].recc_state.float().clone(), dec.caches[1].conv_state.float().clone()))
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][2], outs[1][2])
+    if not bf16_weights:  # and both follow the full-sequence forward
+        full = M.HawkModel(cfg).cuda()
+        full.load_state_dict(model.state_dict())
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            want = full(ids)
+        assert rel_l2(outs[1][0][-1][:, 0], want[:, -1].float()) <= TOL
