@@ -65,10 +65,13 @@ gelu_mul_bwd_kernel(const T* __restrict__ dout, int64_t ldd, const T* __restrict
 }
 
 // ---- RMSNorm: one warp per row, two passes over the row (the second hits L1/L2) ----------------
+// With `delta` the row is first updated, x_out = x + delta (the residual add that precedes every norm
+// in the block, hawk/hawk.py:229-234), and the norm is taken of the sum: one pass instead of two ops.
 template <typename TX, typename TY>
 __global__ void __launch_bounds__(256)
-rms_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
-                    float* __restrict__ rstd, int64_t M, int H, float eps) {
+rms_norm_fwd_kernel(const TX* __restrict__ x, const TY* __restrict__ delta, TX* __restrict__ x_out,
+                    const float* __restrict__ w, TY* __restrict__ y, float* __restrict__ rstd, int64_t M, int H,
+                    float eps) {
   constexpr int VEC = 4;
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -76,11 +79,37 @@ rms_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* _
   for (int64_t m = warp; m < M; m += nwarps) {
     const TX* xr = x + m * H;
     float ss = 0.f;
-    for (int j = lane * VEC; j < H; j += 32 * VEC) {
-      float v[VEC];
-      VecIO<TX, VEC>::load(xr + j, v);
+    if (delta != nullptr) {
+      const TY* dr = delta + m * H;
+      TX* xo = x_out + m * H;
+      for (int j = lane * VEC; j < H; j += 32 * VEC) {
+        float v[VEC], d[VEC];
+        VecIO<TX, VEC>::load(xr + j, v);
+        VecIO<TY, VEC>::load(dr + j, d);
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) ss = fmaf(v[q], v[q], ss);
+        for (int q = 0; q < VEC; ++q) v[q] += d[q];
+        VecIO<TX, VEC>::store(xo + j, v);
+        // statistics of the value as stored (matters when the residual stream itself is bf16)
+        float r[VEC];
+        if (sizeof(TX) == 2) {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) r[q] = __bfloat162float(__float2bfloat16(v[q]));
+        } else {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) r[q] = v[q];
+        }
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) ss = fmaf(r[q], r[q], ss);
+      }
+      __syncwarp();
+      xr = xo;  // second pass reads the sum back (same lanes wrote it)
+    } else {
+      for (int j = lane * VEC; j < H; j += 32 * VEC) {
+        float v[VEC];
+        VecIO<TX, VEC>::load(xr + j, v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) ss = fmaf(v[q], v[q], ss);
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -89,7 +118,19 @@ rms_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* _
     TY* yr = y + m * H;
     for (int j = lane * VEC; j < H; j += 32 * VEC) {
       float v[VEC], wv[VEC], o[VEC];
-      VecIO<TX, VEC>::load(xr + j, v);
+      if (delta != nullptr) {
+        // plain (coherent) loads: these addresses were written by this thread a moment ago
+        if (sizeof(TX) == 2) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(xr + j);
+          const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+          v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
+          const float4 raw = *reinterpret_cast<const float4*>(xr + j);
+          v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+        }
+      } else {
+        VecIO<TX, VEC>::load(xr + j, v);
+      }
       VecIO<float, VEC>::load(w + j, wv);
 #pragma unroll
       for (int q = 0; q < VEC; ++q) o[q] = (v[q] * inv) * wv[q];
@@ -105,8 +146,8 @@ rms_norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* _
 template <typename TX, typename TY, int NCH>
 __global__ void __launch_bounds__(256)
 rms_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
-                    const float* __restrict__ rstd, TX* __restrict__ dx, float* __restrict__ dw_partial, int64_t M,
-                    int H) {
+                    const float* __restrict__ rstd, const TX* __restrict__ gres, TX* __restrict__ dx,
+                    TY* __restrict__ ddelta, float* __restrict__ dw_partial, int64_t M, int H) {
   constexpr int VEC = 4;
   extern __shared__ float red[];  // [warps][H]
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -153,7 +194,14 @@ rms_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x, const f
           o[q] = inv * (gv[q] * wv[q] - xh * cmean);
           acc[c][q] = fmaf(gv[q], xh, acc[c][q]);
         }
+        if (gres != nullptr) {  // gradient arriving at the summed residual from everything after it
+          float gr2[VEC];
+          VecIO<TX, VEC>::load(gres + m * H + j, gr2);
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) o[q] += gr2[q];
+        }
         VecIO<TX, VEC>::store(dr + j, o);
+        if (ddelta != nullptr) VecIO<TY, VEC>::store(ddelta + m * H + j, o);  // same value, delta's dtype
       }
     }
   }
@@ -236,16 +284,17 @@ extern "C" int hawk_gelu_mul_bwd(const void* dout, int64_t ldd, const void* a, i
   return launch_status();
 }
 
-extern "C" int hawk_rms_norm_fwd(const void* x, const float* w, void* y, float* rstd, int64_t M, int H, float eps,
-                                 int x_dtype, int y_dtype, void* stream) {
-  HAWK_REQUIRE(x && w && y && rstd, HAWK_ERR_NULL);
+static int norm_fwd_impl(const void* x, const void* delta, void* x_out, const float* w, void* y, float* rstd,
+                         int64_t M, int H, float eps, int x_dtype, int y_dtype, cudaStream_t st) {
+  HAWK_REQUIRE(x && w && y && rstd && ((delta == nullptr) == (x_out == nullptr)), HAWK_ERR_NULL);
   HAWK_REQUIRE(valid_dtype(x_dtype) && valid_dtype(y_dtype), HAWK_ERR_DTYPE);
   HAWK_REQUIRE(M >= 1 && H >= 4 && H % 4 == 0, HAWK_ERR_SHAPE);
-  HAWK_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 16), HAWK_ERR_ALIGN);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 16) && aligned(delta, 16) && aligned(x_out, 16),
+               HAWK_ERR_ALIGN);
   const unsigned grid = grid_for(M, 8);
-#define HAWK_NORM_FWD(TX, TY)                                                                         \
-  rms_norm_fwd_kernel<TX, TY><<<grid, 256, 0, st>>>(static_cast<const TX*>(x), w, static_cast<TY*>(y), rstd, M, H, eps)
+#define HAWK_NORM_FWD(TX, TY)                                                                                   \
+  rms_norm_fwd_kernel<TX, TY><<<grid, 256, 0, st>>>(static_cast<const TX*>(x), static_cast<const TY*>(delta),    \
+                                                    static_cast<TX*>(x_out), w, static_cast<TY*>(y), rstd, M, H, eps)
   if (x_dtype == HAWK_F32 && y_dtype == HAWK_BF16) HAWK_NORM_FWD(float, bf);
   else if (x_dtype == HAWK_F32) HAWK_NORM_FWD(float, float);
   else if (y_dtype == HAWK_BF16) HAWK_NORM_FWD(bf, bf);
@@ -254,20 +303,32 @@ extern "C" int hawk_rms_norm_fwd(const void* x, const float* w, void* y, float* 
   return launch_status();
 }
 
+extern "C" int hawk_rms_norm_fwd(const void* x, const float* w, void* y, float* rstd, int64_t M, int H, float eps,
+                                 int x_dtype, int y_dtype, void* stream) {
+  return norm_fwd_impl(x, nullptr, nullptr, w, y, rstd, M, H, eps, x_dtype, y_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hawk_add_rms_norm_fwd(const void* x, const void* delta, void* x_out, const float* w, void* y,
+                                     float* rstd, int64_t M, int H, float eps, int x_dtype, int y_dtype,
+                                     void* stream) {
+  HAWK_REQUIRE(delta && x_out, HAWK_ERR_NULL);
+  return norm_fwd_impl(x, delta, x_out, w, y, rstd, M, H, eps, x_dtype, y_dtype, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t hawk_rms_norm_bwd_workspace_bytes(int H) {
   return H < 1 ? 0 : (size_t)kNormBwdCtas * (size_t)H * sizeof(float);
 }
 
-extern "C" int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
-                                 void* workspace, size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
-                                 void* stream) {
+static int norm_bwd_impl(const void* dy, const void* x, const float* w, const float* rstd, const void* gres, void* dx,
+                         void* ddelta, float* dw, void* workspace, size_t workspace_bytes, int64_t M, int H,
+                         int x_dtype, int y_dtype, cudaStream_t st) {
   HAWK_REQUIRE(dy && x && w && rstd && dx && dw, HAWK_ERR_NULL);
   HAWK_REQUIRE(valid_dtype(x_dtype) && valid_dtype(y_dtype), HAWK_ERR_DTYPE);
   HAWK_REQUIRE(M >= 1 && H >= 4 && H % 4 == 0 && H <= 4096, HAWK_ERR_SHAPE);
   HAWK_REQUIRE(workspace && workspace_bytes >= hawk_rms_norm_bwd_workspace_bytes(H), HAWK_ERR_WORKSPACE);
-  HAWK_REQUIRE(aligned(dy, 16) && aligned(x, 16) && aligned(w, 16) && aligned(dx, 16) && aligned(workspace, 16),
+  HAWK_REQUIRE(aligned(dy, 16) && aligned(x, 16) && aligned(w, 16) && aligned(dx, 16) && aligned(workspace, 16) &&
+                   aligned(gres, 16) && aligned(ddelta, 16),
                HAWK_ERR_ALIGN);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
   const int smem = kNormBwdWarps * H * (int)sizeof(float);
   const int nch = (H + 127) / 128;
@@ -279,7 +340,8 @@ extern "C" int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, 
       return HAWK_ERR_LAUNCH;                                                                                       \
     }                                                                                                               \
     kern<<<kNormBwdCtas, kNormBwdWarps * 32, smem, st>>>(static_cast<const TY*>(dy), static_cast<const TX*>(x), w,   \
-                                                         rstd, static_cast<TX*>(dx), partial, M, H);                \
+                                                         rstd, static_cast<const TX*>(gres), static_cast<TX*>(dx),  \
+                                                         static_cast<TY*>(ddelta), partial, M, H);                  \
   } while (0)
 #define HAWK_NORM_BWD(TX, TY)                          \
   do {                                                 \
@@ -297,4 +359,19 @@ extern "C" int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, 
   if (rc != HAWK_OK) return rc;
   rows_sum_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, kNormBwdCtas, H);
   return launch_status();
+}
+
+extern "C" int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
+                                 void* workspace, size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
+                                 void* stream) {
+  return norm_bwd_impl(dy, x, w, rstd, nullptr, dx, nullptr, dw, workspace, workspace_bytes, M, H, x_dtype, y_dtype,
+                       static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hawk_add_rms_norm_bwd(const void* dy, const void* x_sum, const float* w, const float* rstd,
+                                     const void* gres, void* dx, void* ddelta, float* dw, void* workspace,
+                                     size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
+                                     void* stream) {
+  return norm_bwd_impl(dy, x_sum, w, rstd, gres, dx, ddelta, dw, workspace, workspace_bytes, M, H, x_dtype, y_dtype,
+                       static_cast<cudaStream_t>(stream));
 }

@@ -37,6 +37,8 @@ SIGNATURES = {
     "hawk_rms_norm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "hawk_rms_norm_bwd_workspace_bytes": (c_size_t, [c_int]),
     "hawk_rms_norm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int, c_int, c_int, _P]),
+    "hawk_add_rms_norm_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
+    "hawk_add_rms_norm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int, c_int, c_int, _P]),
     "hawk_linear_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "hawk_linear_ce_fwd_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }

@@ -62,10 +62,18 @@ class RMSNorm(nn.Module):
         self.eps = eps
         self.weight = nn.Parameter(torch.ones(dim))
 
-    def forward(self, x):
+    @staticmethod
+    def _out_dtype(x):
         # under autocast the only consumer is a Linear, which would round its input to bf16 anyway
-        out_dtype = torch.bfloat16 if (x.is_cuda and torch.is_autocast_enabled("cuda")) else None
-        return ops.rms_norm(x, self.weight, self.eps, out_dtype=out_dtype)
+        return torch.bfloat16 if (x.is_cuda and torch.is_autocast_enabled("cuda")) else None
+
+    def forward(self, x):
+        return ops.rms_norm(x, self.weight, self.eps, out_dtype=self._out_dtype(x))
+
+    def add_forward(self, residual, delta):
+        """(residual + delta, norm(residual + delta)); delta None = plain norm.  The residual add that
+        precedes every norm (hawk/hawk.py:229,234) is fused into it."""
+        return ops.add_rms_norm(residual, delta, self.weight, self.eps, out_dtype=self._out_dtype(residual))
 
 
 class BlockDiagonalLinear(nn.Module):
@@ -195,11 +203,17 @@ class RNNLayer(nn.Module):
         self.input_norm = RMSNorm(config.hidden_size)
         self.post_recurrent_norm = RMSNorm(config.hidden_size)
 
+    def step(self, residual, pending, layer_past: Optional[RNNCache] = None):
+        """The layer on a residual stream whose last branch output `pending` has not been added yet
+        (None for the first layer).  Returns (residual, pending, cache) in the same form."""
+        residual, normed = self.input_norm.add_forward(residual, pending)
+        mixed, cache = self.recc(normed, layer_past)
+        residual, normed = self.post_recurrent_norm.add_forward(residual, mixed)
+        return residual, self.mlp(normed), cache
+
     def forward(self, hidden_states, layer_past: Optional[RNNCache] = None):
-        mixed, cache = self.recc(self.input_norm(hidden_states), layer_past)
-        hidden_states = hidden_states + mixed
-        hidden_states = hidden_states + self.mlp(self.post_recurrent_norm(hidden_states))
-        return hidden_states, cache
+        residual, pending, cache = self.step(hidden_states, None, layer_past)
+        return residual + pending, cache
 
 
 class HawkModel(nn.Module):
@@ -225,11 +239,12 @@ class HawkModel(nn.Module):
         if layer_past is None:
             layer_past = [None] * len(self.layers)
         hidden = self.embed_tokens(input_ids)
+        pending = None  # branch output not yet added to the residual stream: folded into the next norm
         caches = []
         for layer, past in zip(self.layers, layer_past):
-            hidden, cache = layer(hidden, past)
+            hidden, pending, cache = layer.step(hidden, pending, past)
             caches.append(cache)
-        hidden = self.norm(hidden)
+        _, hidden = self.norm.add_forward(hidden, pending)
         if self.use_cache:
             return self.lm_head(hidden), caches
         if labels is None:

@@ -671,3 +671,92 @@ class _BlockDiagGates(torch.autograd.Function):
 def block_diag_gates(x, wx, bx, wa, ba):
     """(input-gate, recurrence-gate) pre-activations of the RG-LRU from the conv output x [..., R]."""
     return _BlockDiagGates.apply(x, wx, bx, wa, ba)
+
+
+# ---------------------------------------------------------------------------------------------
+# residual add fused into the norm that follows it
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("hawk_b200::add_rms_norm_fwd", mutates_args=())
+def add_rms_norm_fwd(res: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float,
+                     out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(res + delta, rms_norm(res + delta) * w, rstd); delta must have dtype out_dtype."""
+    lib = _lib.load()
+    res, delta, w = res.contiguous(), delta.contiguous(), w.contiguous()
+    H = res.shape[-1]
+    M = res.numel() // H
+    new_res = torch.empty_like(res)
+    y = torch.empty(res.shape, dtype=out_dtype, device=res.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=res.device)
+    with _on(res, "add_rms_norm_fwd", 1):
+        _lib.check(lib.hawk_add_rms_norm_fwd(res.data_ptr(), delta.data_ptr(), new_res.data_ptr(), w.data_ptr(),
+                                             y.data_ptr(), rstd.data_ptr(), M, H, eps, _dt(res), _DT[out_dtype],
+                                             _stream(res)), "hawk_add_rms_norm_fwd")
+    return new_res, y, rstd
+
+
+@add_rms_norm_fwd.register_fake
+def _(res, delta, w, eps, out_dtype):
+    return (torch.empty_like(res, memory_format=torch.contiguous_format), res.new_empty(res.shape, dtype=out_dtype),
+            res.new_empty(res.numel() // res.shape[-1], dtype=torch.float32))
+
+
+@torch.library.custom_op("hawk_b200::add_rms_norm_bwd", mutates_args=())
+def add_rms_norm_bwd(gres: Optional[torch.Tensor], dy: torch.Tensor, x_sum: torch.Tensor, w: torch.Tensor,
+                     rstd: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(d res, d delta, d w): d res = gres + norm-backward(dy); d delta is the same in dy's dtype."""
+    lib = _lib.load()
+    dy, x_sum, w = dy.contiguous(), x_sum.contiguous(), w.contiguous()
+    if gres is not None:
+        gres = gres.contiguous()
+    H = x_sum.shape[-1]
+    M = x_sum.numel() // H
+    dx = torch.empty_like(x_sum)
+    ddelta = torch.empty(x_sum.shape, dtype=dy.dtype, device=x_sum.device)
+    dw = torch.empty(H, dtype=torch.float32, device=x_sum.device)
+    ws_bytes = lib.hawk_rms_norm_bwd_workspace_bytes(H)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x_sum.device)
+    with _on(x_sum, "add_rms_norm_bwd", 2):
+        _lib.check(lib.hawk_add_rms_norm_bwd(dy.data_ptr(), x_sum.data_ptr(), w.data_ptr(), rstd.data_ptr(), _ptr(gres),
+                                             dx.data_ptr(), ddelta.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws_bytes,
+                                             M, H, _dt(x_sum), _dt(dy), _stream(x_sum)), "hawk_add_rms_norm_bwd")
+    return dx, ddelta, dw
+
+
+@add_rms_norm_bwd.register_fake
+def _(gres, dy, x_sum, w, rstd):
+    return (torch.empty_like(x_sum), x_sum.new_empty(x_sum.shape, dtype=dy.dtype),
+            w.new_empty(w.shape, dtype=torch.float32))
+
+
+def _arn_setup(ctx, inputs, output):
+    _, delta, w, _, _ = inputs
+    new_res, _, rstd = output
+    ctx.save_for_backward(new_res, w, rstd)
+    ctx.w_dtype, ctx.delta_dtype = w.dtype, delta.dtype
+    ctx.set_materialize_grads(False)
+
+
+def _arn_backward(ctx, g_res, g_y, g_rstd):
+    new_res, w, rstd = ctx.saved_tensors
+    if g_y is None:  # the norm output was not used: only the residual path carries gradient
+        if g_res is None:
+            return None, None, None, None, None
+        return g_res, g_res.to(ctx.delta_dtype), None, None, None
+    dx, ddelta, dw = add_rms_norm_bwd(g_res, g_y, new_res, w, rstd)
+    return dx, ddelta, dw.to(ctx.w_dtype), None, None
+
+
+add_rms_norm_fwd.register_autograd(_arn_backward, setup_context=_arn_setup)
+
+
+def add_rms_norm(res, delta, weight, eps: float = 1e-6, out_dtype=None):
+    """(res + delta, rms_norm(res + delta) * weight): the block's residual add and the norm after it in
+    one pass each way.  `delta` None means a plain norm of `res`."""
+    out_dtype = out_dtype or res.dtype
+    w32 = weight if weight.dtype == torch.float32 else weight.float()
+    if delta is None:
+        return res, rms_norm_fwd(res, w32, eps, out_dtype)[0]
+    if delta.dtype != out_dtype:
+        delta = delta.to(out_dtype)
+    new_res, y, _ = add_rms_norm_fwd(res, delta, w32, eps, out_dtype)
+    return new_res, y

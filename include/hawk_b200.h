@@ -166,6 +166,16 @@ int hawk_rms_norm_bwd(const void* dy, const void* x, const float* w, const float
                       void* workspace, size_t workspace_bytes, int64_t M, int H, int x_dtype, int y_dtype,
                       void* stream);
 
+/* The residual add that precedes every norm of the block (hawk/hawk.py:229,234 followed by :227,232,284)
+ * fused into the norm: x_out = x + delta (x_dtype; delta in y_dtype), y = rms_norm(x_out).  Backward:
+ * dx = gres + (norm backward of dy), with gres the gradient reaching x_out from everything after it
+ * (x_dtype, may be NULL); ddelta (y_dtype, may be NULL) receives the same values for the delta branch. */
+int hawk_add_rms_norm_fwd(const void* x, const void* delta, void* x_out, const float* w, void* y, float* rstd,
+                          int64_t M, int H, float eps, int x_dtype, int y_dtype, void* stream);
+int hawk_add_rms_norm_bwd(const void* dy, const void* x_sum, const float* w, const float* rstd, const void* gres,
+                          void* dx, void* ddelta, float* dw, void* workspace, size_t workspace_bytes, int64_t M,
+                          int H, int x_dtype, int y_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -98,3 +98,43 @@ def test_block_diag_gates_match_einsum(dtype, nb, bw, lead):
     assert rel_l2(xd.grad.float().cpu(), xr.grad) <= tol
     for a, b in zip(pd, pr):
         assert rel_l2(a.grad.cpu(), b.grad) <= tol
+
+
+@pytest.mark.parametrize("xdt,ydt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                     (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("M,H", [(5, 64), (300, 2048)])
+def test_add_rms_norm_matches_torch(xdt, ydt, M, H):
+    """Fused residual add + norm: both outputs and all three gradients, with gradient arriving on the
+    summed residual as well as on the norm output."""
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(M * 7 + H)
+    res = (2 * torch.randn(M, H, generator=g)).to(xdt)
+    delta = torch.randn(M, H, generator=g).to(ydt)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    g_y = torch.randn(M, H, generator=g).to(ydt)
+    g_r = torch.randn(M, H, generator=g).to(xdt)
+    rr, dr, wr = res.double().requires_grad_(True), delta.double().requires_grad_(True), w.double().requires_grad_(True)
+    s = rr + dr
+    if xdt == torch.bfloat16:
+        s = s + (s.detach().bfloat16().double() - s.detach())  # the stream is stored in bf16
+    yr = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    torch.autograd.backward([s, yr], [g_r.double(), g_y.double()])
+    rd, dd, wd = res.cuda().requires_grad_(True), delta.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    new_res, y = ops.add_rms_norm(rd, dd, wd, 1e-6, out_dtype=ydt)
+    assert new_res.dtype == xdt and y.dtype == ydt
+    torch.autograd.backward([new_res, y], [g_r.cuda(), g_y.cuda()])
+    tol = 1e-5 if (xdt == torch.float32 and ydt == torch.float32) else 2e-2
+    assert rel_l2(new_res.float().cpu(), s.detach()) <= (1e-6 if xdt == torch.float32 else 1e-2)
+    assert rel_l2(y.float().cpu(), yr.detach()) <= tol
+    assert rel_l2(rd.grad.float().cpu(), rr.grad) <= tol
+    assert rel_l2(dd.grad.float().cpu(), dr.grad) <= tol
+    assert rel_l2(wd.grad.cpu(), wr.grad) <= tol
+    # residual-only gradient (norm output unused) and norm-only gradient (sum unused)
+    rd2, dd2 = res.cuda().requires_grad_(True), delta.cuda().requires_grad_(True)
+    nr2, y2 = ops.add_rms_norm(rd2, dd2, wd.detach(), 1e-6, out_dtype=ydt)
+    nr2.backward(g_r.cuda())
+    assert rel_l2(rd2.grad.float().cpu(), g_r.double()) <= 1e-6
+    rd3, dd3 = res.cuda().requires_grad_(True), delta.cuda().requires_grad_(True)
+    _, y3 = ops.add_rms_norm(rd3, dd3, wd.detach(), 1e-6, out_dtype=ydt)
+    y3.backward(g_y.cuda())
+    assert torch.isfinite(rd3.grad).all() and rel_l2(dd3.grad.float().cpu(), rd3.grad.float().cpu()) <= 1e-2
