@@ -236,7 +236,8 @@ def run_ours(args):
             entry["unit"] = unit
         kernels[k] = entry
 
-    cpu_tps, cpu_step = cpu_oracle_tokens_per_sec(steps=2, warmup=1) if world == 1 else (None, None)
+    run_cpu = world == 1 and not args.no_cpu_baseline
+    cpu_tps, cpu_step = cpu_oracle_tokens_per_sec(steps=2, warmup=1) if run_cpu else (None, None)
     line = {
         "metric": "hawk_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms_total / steps, "higher_is_better": True,
@@ -264,6 +265,8 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true",
+                    help="skip the CPU-oracle leg (e.g. when the command runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
