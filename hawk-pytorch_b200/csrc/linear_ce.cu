@@ -27,9 +27,20 @@
 
 namespace hawk {
 
-constexpr int BM = 128, BN = 256, BK = 64, KSTAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES_G = A_BYTES + B_BYTES;
-constexpr int GEMM_SMEM = KSTAGES * STAGE_BYTES_G + 1024;  // + slack for 1024-byte alignment
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;  // one tcgen05.mma covers 128 x 256 x 16
+constexpr int A_HALF_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+// MH = number of 128-row halves per CTA tile.  MH = 1: 128x256 tile, two TMEM accumulators (the
+// epilogue overlaps the next tile), 4 stages.  MH = 2: 256x256 tile (both halves share the B tile, so
+// operand traffic per flop drops by a third), the two halves fill TMEM, 3 stages; used for the
+// long-K gradient GEMMs, where the un-overlapped epilogue is a few percent of a tile.
+template <int MH>
+struct GemmCfg {
+  static constexpr int STAGES = MH == 1 ? 4 : 3;
+  static constexpr int A_BYTES = MH * A_HALF_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+  static constexpr int NACC = MH == 1 ? 2 : 1;
+};
 constexpr int GEMM_THREADS = 192;
 constexpr long long WAIT_BUDGET = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
@@ -162,9 +173,12 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 // ---------------------------------------------------------------------------------------------
 // the GEMM
 // ---------------------------------------------------------------------------------------------
+template <int MH>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     int K, int m_tiles, int n_tiles, EpiParams ep, int* status) {
+  using Cfg = GemmCfg<MH>;
+  constexpr int KSTAGES = Cfg::STAGES, STAGE_BYTES_G = Cfg::STAGE_BYTES, A_BYTES = Cfg::A_BYTES, NACC = Cfg::NACC;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[KSTAGES], empty_bar[KSTAGES], tfull_bar[2], tempty_bar[2];
@@ -207,7 +221,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) break;
           mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES_G);
           unsigned char* st = smem + s * STAGE_BYTES_G;
-          tma_load_2d(st, &map_a, &full_bar[s], kb * BK, mt * BM);
+          tma_load_2d(st, &map_a, &full_bar[s], kb * BK, mt * BM * MH);
           tma_load_2d(st + A_BYTES, &map_b, &full_bar[s], kb * BK, nt * BN);
         }
       }
@@ -217,8 +231,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abortp; tile += gridDim.x, ++tcount) {
-        const int acc = tcount & 1;
-        const uint32_t aph = (tcount >> 1) & 1;
+        const int acc = NACC == 2 ? (tcount & 1) : 0;
+        const uint32_t aph = NACC == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abortp)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -232,8 +246,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16(d_tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2),
-                      (kb | k) ? 1u : 0u);
+#pragma unroll
+            for (int hh = 0; hh < MH; ++hh) {  // the halves of a 256-row tile accumulate side by side in TMEM
+              umma_bf16(d_tmem + hh * BN, umma_desc(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 2),
+                        umma_desc(b_addr + k * UMMA_K * 2), (kb | k) ? 1u : 0u);
+            }
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
         }
@@ -249,14 +266,16 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (*abortp) break;
       int mt, nt;
       tile_coords(tile, m_tiles, n_tiles, mt, nt);
-      const int acc = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1;
+      const int acc = NACC == 2 ? (tcount & 1) : 0;
+      const uint32_t aph = NACC == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
       if (!mbar_wait(&tfull_bar[acc], aph, abortp)) break;
       tc_fence_after();
-      const int row = mt * BM + quarter * 32 + lane;
-      const bool row_ok = row < ep.M;
-      const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const int col0 = nt * BN;
+#pragma unroll 1
+      for (int hh = 0; hh < MH; ++hh) {
+      const int row = (mt * MH + hh) * BM + quarter * 32 + lane;
+      const bool row_ok = row < ep.M;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((acc + hh) * BN);
 
       if (ep.mode == EPI_LOGITS) {
         float run_m = -INFINITY, run_s = 0.f;
@@ -323,6 +342,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      }  // halves
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -523,18 +543,20 @@ static int sm_count() {
 }
 
 // C[M, Nc] = A[M, K] . B[Nc, K]^T  (A, B bf16 row-major with pitches lda, ldb)
+template <int MH>
 static int launch_gemm(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* B, long long ldb, int M, int Nc, int K,
                        const EpiParams& ep, int* status, cudaStream_t st) {
+  using Cfg = GemmCfg<MH>;
   CUtensorMap ma, mb;
-  if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, B, Nc, K, ldb, BN)) return HAWK_ERR_DEVICE;
+  if (!make_map(&ma, A, M, K, lda, BM * MH) || !make_map(&mb, B, Nc, K, ldb, BN)) return HAWK_ERR_DEVICE;
   // per call: the attribute belongs to the current device's copy of the kernel
-  if (cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) {
+  if (cudaFuncSetAttribute(gemm_bf16_tn_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
     (void)cudaGetLastError();
     return HAWK_ERR_LAUNCH;
   }
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (Nc + BN - 1) / BN;
+  const int m_tiles = (M + BM * MH - 1) / (BM * MH), n_tiles = (Nc + BN - 1) / BN;
   const int grid = min(m_tiles * n_tiles, sm_count());
-  gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, K, m_tiles, n_tiles, ep, status);
+  gemm_bf16_tn_kernel<MH><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ma, mb, K, m_tiles, n_tiles, ep, status);
   return launch_status();
 }
 
@@ -627,7 +649,7 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     ep.stats = stats;
     ep.correct = correct;
     ep.labels = reinterpret_cast<const long long*>(labels);
-    int rc = launch_gemm(ab, H, wb, H, (int)N, (int)V, (int)H, ep, status, st);
+    int rc = launch_gemm<1>(ab, H, wb, H, (int)N, (int)V, (int)H, ep, status, st);
     if (rc != HAWK_OK) return rc;
   }
   // 3. log-sum-exp per row and the mean loss
@@ -649,11 +671,11 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     ep.Nc = (int)H;
     ep.out = dact;
     ep.ldo = H;
-    int rc = launch_gemm(logits, L.ldV, wbT, L.ldV, (int)N, (int)H, (int)V, ep, status, st);
+    int rc = launch_gemm<2>(logits, L.ldV, wbT, L.ldV, (int)N, (int)H, (int)V, ep, status, st);
     if (rc != HAWK_OK) return rc;
     ep.M = (int)V;
     ep.out = dweight;
-    rc = launch_gemm(dpT, L.ldN, abT, L.ldN, (int)V, (int)H, (int)N, ep, status, st);
+    rc = launch_gemm<2>(dpT, L.ldN, abT, L.ldN, (int)V, (int)H, (int)N, ep, status, st);
     if (rc != HAWK_OK) return rc;
   }
   return HAWK_OK;
