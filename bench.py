@@ -41,9 +41,10 @@ B_PER_GPU, SEQ_LEN, VOCAB = 8, 4096, 32000
 CPU_SAMPLE_B, CPU_SAMPLE_T = 1, 128
 WORKLOAD = ("hawk_1b_train_step: vocab 32000, hidden 2048, recurrent 2048, intermediate 6144, 24 layers, "
             "16 gate blocks, conv width 4; per-GPU B=8, T=4096; bf16 autocast, fused linear-CE, AdamW")
-# DRAM bytes (read + write) of one scan forward / backward launch at B=8, T=4096, D=2048 bf16, from the
-# ncu capture summarised in profiles/scan_B8_T4096_D2048_bf16.md
-SCAN_TRAFFIC_BYTES = None
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one scan forward plus one scan backward
+# launch at B=8, T=4096, D=2048 bf16, from the ncu capture summarised in profiles/scan_B8_D2048_bf16.md
+# (forward 405.2 + 110.5 MB, backward 671.1 + 364.9 MB; part of the output is still in L2 at kernel end)
+SCAN_TRAFFIC_BYTES = 515_724_288 + 1_036_071_168
 
 
 def measured_hbm_peak():
