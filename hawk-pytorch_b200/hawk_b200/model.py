@@ -152,19 +152,31 @@ class Hawk(nn.Module):
         self.rg_lru_a_param = nn.Parameter(torch.empty(R, dtype=torch.float32))
         self.resid_proj = nn.Linear(R, config.hidden_size, bias=False)
         self.conv1d = ops.Conv1D(width=R, temporal_width=config.conv_width)
+        self._fp32_cache = {}
         ring_init_(self.rg_lru_a_param)
         _lecun_normal_(self.input_xy.weight, config.hidden_size)
         nn.init.zeros_(self.resid_proj.weight)
+
+    def _fp32(self, name: str, p: torch.Tensor) -> torch.Tensor:
+        """fp32 view of a small parameter for the kernels that take fp32 taps / Lambda; when the model
+        has been cast to bf16 the converted copy is kept until the parameter changes."""
+        if p.dtype == torch.float32:
+            return p
+        hit = self._fp32_cache.get(name)
+        if hit is None or hit[0] != p._version or hit[1].device != p.device:
+            hit = (p._version, p.detach().float())
+            self._fp32_cache[name] = hit
+        return hit[1]
 
     def _decode(self, xb, y, cache: RNNCache):
         """One cached token: xb, y [B,1,R] (hawk/hawk.py:168-179,193-199)."""
         x_new = xb[:, 0]
         conv = self.conv1d
-        xc = ops.decode_conv_step(x_new, cache.conv_state, conv.w.float(), conv.b.float())
-        gx = self.rg_lru_input_gate(xc)
-        ga = self.rg_lru_a_gate(xc)
+        xc = ops.decode_conv_step(x_new, cache.conv_state, self._fp32("w", conv.w), self._fp32("b", conv.b))
+        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, self.rg_lru_input_gate.b,
+                                      self.rg_lru_a_gate.w, self.rg_lru_a_gate.b)
         state = cache.recc_state[:, 0]
-        h = ops.decode_rglru_step(xc, gx.to(xc.dtype), ga.to(xc.dtype), self.rg_lru_a_param.float(), state)
+        h = ops.decode_rglru_step(xc, gx, ga, self._fp32("lam", self.rg_lru_a_param), state)
         cache.current_cache_size = 1
         return self.resid_proj(ops.gelu_mul(y, h[:, None]))
 
