@@ -14,6 +14,7 @@ One JSON line is printed by rank 0:
   roofline   the RG-LRU scan forward+backward: algorithmic bytes (24 B/element in bf16) over the mean
              CUDA-event time of the scan launches INSIDE the timed training steps, against the
              measured HBM copy bandwidth of this pool (MEASURED_PEAKS.json, else the 6650 GB/s fallback);
+             `isolated` repeats the measurement on the same kernels outside the step (N = 1 only);
   kernels    mean device time and derived rate of each of this library's entry points in the same steps;
   cpu_baseline   the CPU oracle of the same model (oracle/model.py) timed on the host cores on a
              bounded sample (B=1, T=128 per step).
@@ -215,6 +216,27 @@ def run_ours(args):
     if rank != 0:
         return 0
 
+    # the same two kernels alone, back to back on resident tensors (no GEMMs around them drawing power)
+    isolated = None
+    if world == 1:
+        del ids_buf
+        g2 = torch.Generator(device=dev).manual_seed(7)
+        xs = [torch.randn(B_PER_GPU, SEQ_LEN, 2048, generator=g2, device=dev).bfloat16() for _ in range(4)]
+        lam = trainer.model.layers[0].recc.rg_lru_a_param.detach().float()
+        h = ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
+        for _ in range(3):
+            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
+            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, h, xs[3])
+        ops.LOG.reset(enabled=True, timed=True)
+        for _ in range(20):
+            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
+        for _ in range(20):
+            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, h, xs[3])
+        torch.cuda.synchronize()
+        isolated = {"fwd_ms": ops.LOG.mean_ms("scan_fwd"), "bwd_ms": ops.LOG.mean_ms("scan_bwd")}
+        ops.LOG.reset(enabled=False)
+        del xs, h
+
     n_elem = B_PER_GPU * SEQ_LEN * 2048
     peak, peak_src = measured_hbm_peak()
     roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
@@ -225,6 +247,11 @@ def run_ours(args):
         roofline["achieved"] = 24 * n_elem / t / 1e9
         roofline["frac"] = roofline["achieved"] / peak
         roofline["launch_ms"] = {"fwd": kernel_ms["scan_fwd"], "bwd": kernel_ms["scan_bwd"]}
+    if isolated:
+        t = (isolated["fwd_ms"] + isolated["bwd_ms"]) * 1e-3
+        roofline["isolated"] = {"achieved": 24 * n_elem / t / 1e9, "frac": 24 * n_elem / t / 1e9 / peak,
+                                "launch_ms": {"fwd": isolated["fwd_ms"], "bwd": isolated["bwd_ms"]},
+                                "note": "same kernels and shape, 20 back-to-back launches each outside the step"}
     kernels = {}
     n_ce = B_PER_GPU * (SEQ_LEN - 1)
     rates = {"scan_fwd": (8 * n_elem, "GB/s"), "scan_bwd": (16 * n_elem, "GB/s"), "conv1d_fwd": (4 * n_elem, "GB/s"),

@@ -617,9 +617,6 @@ extern "C" int hawk_scan_fwd(const void* x, const void* gx, const void* ga, cons
       case 3: HAWK_FWD(bf, 8, 4, 8, 2, 7, true);
       case 4: HAWK_FWD(bf, 8, 4, 8, 4, 4, true);
       case 5: HAWK_FWD(bf, 4, 4, 8, 4, 7, true);
-      case 6: HAWK_FWD(bf, 4, 16, 32, 2, 2, true);
-      case 7: HAWK_FWD(bf, 4, 16, 32, 4, 2, true);
-      case 8: HAWK_FWD(bf, 8, 8, 32, 2, 2, true);
       default: return HAWK_ERR_UNSUPPORTED;
     }
   }

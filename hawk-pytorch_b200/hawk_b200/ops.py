@@ -7,7 +7,8 @@ place of its own (hawk/hawk.py:12-14):
     Conv1D(width, temporal_width, w_init_variance_scale)(x) -> y   hawk/external.py:12-98
     fused_cross_entropy(lm_head_weight, act, labels) -> loss       hawk/fused_cross_entropy.py:77-79
 
-plus the two halves of the cached decode step (hawk/hawk.py:137-151,168-199).
+plus the two halves of the cached decode step (hawk/hawk.py:137-151,168-199) and the block's glue in
+single passes: gelu(a) * b, RMSNorm with the preceding residual add, the block-diagonal gate pair.
 
 Each op is a torch.library custom op (with a fake/meta kernel and a registered backward), so
 torch.compile treats it as an opaque call; the real implementation hands raw device pointers

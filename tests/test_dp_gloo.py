@@ -4,7 +4,6 @@ import os
 import subprocess
 import sys
 
-import pytest
 import torch
 
 from conftest import ROOT, max_rel

@@ -8,7 +8,7 @@ import math
 import pytest
 import torch
 
-from conftest import load_golden, max_rel, rel_l2
+from conftest import load_golden, rel_l2
 from oracle import model as omodel
 
 pytestmark = pytest.mark.gpu
