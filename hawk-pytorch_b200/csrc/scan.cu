@@ -575,13 +575,16 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
 }
 
 // Launch shape.  A CTA scans all of T for its channel group, so the grid is B * D / CW CTAs of equal
-// cost.  Measured on B200 (bf16): the forward is fastest with narrow groups (CW = 16, 128-thread
-// CTAs, ~7 per SM) at every shape tried; the backward with CW = 64 and 8 rows per slot when there
-// are enough (batch x group) pairs to fill the SMs, else with CW = 32 to double the CTA count.
+// cost.  Measured on B200 (bf16), alone and inside a training step (where the SM clock sits near
+// 1.55 GHz under the board's power limit and the kernels turn compute bound): the forward is best
+// with narrow groups (CW = 16, 128-thread CTAs, ~7 per SM: even load on every SM), the backward with
+// CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
+// with CW = 32 to double the CTA count.
 static int pick_cfg(int B, int D, bool backward) {
   if (const char* e = getenv("HAWK_SCAN_CFG")) return atoi(e);  // tuning/debug override
-  if (!backward) return 3;
-  return (int64_t)B * (D / 64) >= 200 ? 5 : 1;
+  const bool many = (int64_t)B * (D / 64) >= 200;
+  if (!backward) return many ? 3 : 4;
+  return many ? 5 : 1;
 }
 
 static int check_scan_common(int B, int T, int D, int dtype) {
