@@ -70,3 +70,31 @@ def test_ops_refuse_cpu_tensors():
     x = torch.zeros(1, 4, 64)
     with pytest.raises(RuntimeError, match="CUDA"):
         fused_linear_scan(x, x, x, torch.zeros(64))
+
+
+def test_glue_ce_and_decode_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)
+    # gelu_mul: width and pitches in multiples of 8, pitch >= width
+    assert lib.hawk_gelu_mul_fwd(p, 64, p, 64, p, 64, 4, 60, 1, None) == -2
+    assert lib.hawk_gelu_mul_fwd(p, 32, p, 64, p, 64, 4, 64, 1, None) == -2
+    assert lib.hawk_gelu_mul_fwd(p, 68, p, 64, p, 64, 4, 64, 1, None) == -4
+    assert lib.hawk_gelu_mul_bwd(p, 64, p, 64, p, 64, None, 64, p, 64, 4, 64, 1, None) == -1
+    # rms_norm: H % 4, backward H <= 4096, workspace
+    assert lib.hawk_rms_norm_fwd(p, p, p, p, 4, 66, 1e-6, 0, 1, None) == -2
+    assert lib.hawk_rms_norm_bwd_workspace_bytes(2048) == 296 * 2048 * 4
+    assert lib.hawk_rms_norm_bwd(p, p, p, p, p, p, p, 1 << 30, 4, 8192, 0, 1, None) == -2
+    assert lib.hawk_rms_norm_bwd(p, p, p, p, p, p, p, 16, 4, 2048, 0, 1, None) == -5
+    assert lib.hawk_add_rms_norm_fwd(p, None, p, p, p, p, 4, 64, 1e-6, 0, 1, None) == -1
+    # linear cross-entropy: H % 8, workspace size, alignment
+    assert lib.hawk_linear_ce_fwd_bwd(p, p, p, p, p, p, p, 1 << 40, 16, 60, 100, 0, p, None) == -2
+    need = lib.hawk_linear_ce_workspace_bytes(16, 64, 100)
+    assert need > 16 * 100 * 2 * 2
+    assert lib.hawk_linear_ce_fwd_bwd(p, p, p, p, p, p, p, need - 1, 16, 64, 100, 0, p, None) == -5
+    assert lib.hawk_linear_ce_fwd_bwd(p, p, p, p, p, p, ctypes.c_void_p(4096 + 64), need, 16, 64, 100, 0, p, None) == -4
+    # decode steps
+    assert lib.hawk_decode_conv_step(p, 64, p, p, p, p, 2, 60, 4, 1, 1, None) == -2
+    assert lib.hawk_decode_conv_step(p, 64, p, p, p, p, 2, 64, 5, 1, 1, None) == -7
+    assert lib.hawk_decode_rglru_step(p, p, p, p, None, p, 2, 64, 1, 1, None) == -1
+    # the no-allocation backward refuses what its built-in scratch cannot hold
+    assert lib.hawk_scan_bwd_noalloc(p, p, p, p, None, p, p, p, p, p, p, None, 129, 8, 2048, 1, None) == -9
