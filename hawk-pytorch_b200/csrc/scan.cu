@@ -103,7 +103,8 @@ __device__ __forceinline__ void gates2(float2 gx, float2 ga, float2& i, float2& 
 }
 
 // a = exp(k r) for both channels (k already in log2 units on the FAST path).
-// (Moving this exponential onto the FMA pipe as a polynomial was measured: same kernel time.)
+// (Moving this exponential onto the FMA pipe as a polynomial was measured, alone and inside a training
+// step: never faster.)
 template <bool FAST>
 __device__ __forceinline__ float2 decay2(float2 k, float2 r) {
   if (FAST) {
