@@ -40,11 +40,20 @@ struct SmemPair;  // two adjacent channels read back from the staging ring
 template <>
 struct SmemPair<float> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p) { return ld(p); }
 };
 template <>
 struct SmemPair<__nv_bfloat16> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) {
     return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
+  }
+  // gate pre-activations, floored at -29 while still packed (one max.bf16x2 for both channels):
+  // sigmoid(-29) is 2.5e-13 already, and the floor keeps 2^(-g log2 e) and the shared reciprocal of
+  // the bf16 path finite without per-channel clamps
+  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p) {
+    uint32_t v = *reinterpret_cast<const uint32_t*>(p), r;
+    asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0xC1E8C1E8u));  // -29.0 in both halves
+    return unpack_bf16x2(r);
   }
 };
 
@@ -86,10 +95,10 @@ template <bool FAST>
 __device__ __forceinline__ void gates2(float2 gx, float2 ga, float2& i, float2& r) {
   if (FAST) {
     float2 tx = mul2(gx, f2(-kLog2e)), ta = mul2(ga, f2(-kLog2e));
-    tx.x = ex2_approx(fminf(tx.x, 43.f));
-    tx.y = ex2_approx(fminf(tx.y, 43.f));
-    ta.x = ex2_approx(fminf(ta.x, 43.f));
-    ta.y = ex2_approx(fminf(ta.y, 43.f));
+    tx.x = ex2_approx(tx.x);  // inputs were floored at -29 when loaded (SmemPair::ld_gate)
+    tx.y = ex2_approx(tx.y);
+    ta.x = ex2_approx(ta.x);
+    ta.y = ex2_approx(ta.y);
     const float2 u = add2(tx, f2(1.f)), v = add2(ta, f2(1.f));
     float2 w = mul2(u, v);
     w.x = rcp_approx(w.x);
@@ -133,10 +142,10 @@ __device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, floa
     gates2<true>(gx, ga, i, r);
     a = decay2<true>(k, r);
     const float2 v = fma2(neg2(a), a, f2(1.f));
-    float2 rs;
-    rs.x = rsqrt_approx(fmaxf(v.x, 1e-30f));  // sqrt(v) = v * rsqrt(v), one MUFU operation
-    rs.y = rsqrt_approx(fmaxf(v.y, 1e-30f));
-    beta = mul2(mul2(x, i), mul2(v, rs));
+    float2 m;
+    m.x = sqrt_approx(v.x);
+    m.y = sqrt_approx(v.y);
+    beta = mul2(mul2(x, i), m);
   } else {
     fwd_coeffs<false>(x.x, gx.x, ga.x, k.x, a.x, beta.x);
     fwd_coeffs<false>(x.y, gx.y, ga.y, k.y, a.y, beta.y);
@@ -279,8 +288,8 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     for (int r = 0; r < R; ++r) {
       if (FULL || t0 + r < T_len) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
-        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld(row + G::IN_BYTES),
-                          SmemPair<T>::ld(row + 2 * G::IN_BYTES), k2, a[r], be[r]);
+        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld_gate(row + G::IN_BYTES),
+                          SmemPair<T>::ld_gate(row + 2 * G::IN_BYTES), k2, a[r], be[r]);
       } else {  // past the end: identity step
         a[r] = f2(1.f);
         be[r] = f2(0.f);
@@ -417,7 +426,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       if (FULL || tt - r >= 0) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
         gov = SmemPair<T>::ld(row + G::IN_BYTES);
-        gates2<FAST>(SmemPair<T>::ld(row + 3 * G::IN_BYTES), SmemPair<T>::ld(row), ig[r], rg[r]);
+        gates2<FAST>(SmemPair<T>::ld_gate(row + 3 * G::IN_BYTES), SmemPair<T>::ld_gate(row), ig[r], rg[r]);
         a[r] = decay2<FAST>(k2, rg[r]);
       } else {
         rg[r] = ig[r] = f2(0.f);
