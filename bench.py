@@ -223,15 +223,18 @@ def run_ours(args):
         g2 = torch.Generator(device=dev).manual_seed(7)
         xs = [torch.randn(B_PER_GPU, SEQ_LEN, 2048, generator=g2, device=dev).bfloat16() for _ in range(4)]
         lam = trainer.model.layers[0].recc.rg_lru_a_param.detach().float()
-        h = ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
+        gb = 0.1 * torch.randn(2, 2048, generator=g2, device=dev)  # gate biases, as the training step passes them
+        h = ops.scan_fwd(xs[0], xs[1], xs[2], lam, None, gb)
         for _ in range(3):
-            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
-            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, h, xs[3])
+            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None, gb)
+            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, gb, h, xs[3])
+        torch.cuda.synchronize()
+        time.sleep(3.0)  # let the board leave the power-capped state of the training loop: a burst figure
         ops.LOG.reset(enabled=True, timed=True)
         for _ in range(20):
-            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None)
+            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None, gb)
         for _ in range(20):
-            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, h, xs[3])
+            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, gb, h, xs[3])
         torch.cuda.synchronize()
         isolated = {"fwd_ms": ops.LOG.mean_ms("scan_fwd"), "bwd_ms": ops.LOG.mean_ms("scan_bwd")}
         ops.LOG.reset(enabled=False)
@@ -251,7 +254,7 @@ def run_ours(args):
         t = (isolated["fwd_ms"] + isolated["bwd_ms"]) * 1e-3
         roofline["isolated"] = {"achieved": 24 * n_elem / t / 1e9, "frac": 24 * n_elem / t / 1e9 / peak,
                                 "launch_ms": {"fwd": isolated["fwd_ms"], "bwd": isolated["bwd_ms"]},
-                                "note": "same kernels and shape, 20 back-to-back launches each outside the step"}
+                                "note": "same kernels and shape, 20 back-to-back launches each outside the step, after 3 s idle (burst clocks)"}
     kernels = {}
     n_ce = B_PER_GPU * (SEQ_LEN - 1)
     rates = {"scan_fwd": (8 * n_elem, "GB/s"), "scan_bwd": (16 * n_elem, "GB/s"), "conv1d_fwd": (4 * n_elem, "GB/s"),

@@ -37,23 +37,30 @@ __device__ __forceinline__ void cp_async_wait() {
 
 template <typename T>
 struct SmemPair;  // two adjacent channels read back from the staging ring
+// ld_gate reads a gate pre-activation pair g.  The bf16 path floors it, while still packed (one
+// max.bf16x2 for both channels), at the lane's constant from gate_floor(): -42 - bias, so that
+// g + bias >= -42.4 whatever the bias is.  sigmoid(-42) is 6e-19 already, and the floor keeps
+// 2^(-(g + bias) log2 e) below 2^62 and the shared reciprocal of the two gates' product finite
+// without per-channel clamps.  The fp32 path uses expf and needs no floor.
 template <>
 struct SmemPair<float> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
-  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p) { return ld(p); }
+  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p, uint32_t) { return ld(p); }
+  static __device__ __forceinline__ uint32_t gate_floor(float, float) { return 0u; }
 };
 template <>
 struct SmemPair<__nv_bfloat16> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) {
     return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
   }
-  // gate pre-activations, floored at -29 while still packed (one max.bf16x2 for both channels):
-  // sigmoid(-29) is 2.5e-13 already, and the floor keeps 2^(-g log2 e) and the shared reciprocal of
-  // the bf16 path finite without per-channel clamps
-  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p) {
+  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p, uint32_t floor2) {
     uint32_t v = *reinterpret_cast<const uint32_t*>(p), r;
-    asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0xC1E8C1E8u));  // -29.0 in both halves
+    asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(floor2));
     return unpack_bf16x2(r);
+  }
+  // b0, b1: the lane's two bias values (0 without a bias); rounding to bf16 moves the floor by < 0.4
+  static __device__ __forceinline__ uint32_t gate_floor(float b0, float b1) {
+    return pack_bf16x2(-42.f - b0, -42.f - b1);
   }
 };
 
@@ -62,6 +69,23 @@ __device__ __forceinline__ float gate_scale(float lam) {
   // per-channel constant k with log_a = k * r  (FAST: in log2 units)
   const float sp = lam > 20.f ? lam : softplus_f(lam);
   return FAST ? kGateC * sp * kLog2e : kGateC * sp;
+}
+
+// The lane's gate-bias pair [bias of channel ch, of ch+1] from row `row` of the optional [2, D] table:
+// `term` in the form gates2 consumes, `floor2` for SmemPair::ld_gate.  FAST folds the bias into the
+// multiply that feeds 2^x, so the add costs no instruction: -log2(e) (g + b) = fma(g, -log2 e,
+// -log2(e) b).  The sum is not rounded to the storage type (the reference rounds gate + bias to bf16
+// before its scan, hawk/scan_fused.py:428).
+template <typename T, bool FAST>
+__device__ __forceinline__ void gate_bias_term(const float* __restrict__ gbias, int row, int D, int ch,
+                                               float2& term, uint32_t& floor2) {
+  float b0 = 0.f, b1 = 0.f;
+  if (gbias != nullptr) {
+    b0 = gbias[(size_t)row * D + ch];
+    b1 = gbias[(size_t)row * D + ch + 1];
+  }
+  term = FAST ? make_float2(-kLog2e * b0, -kLog2e * b1) : make_float2(b0, b1);
+  floor2 = SmemPair<T>::gate_floor(b0, b1);
 }
 
 // ---- arithmetic on a lane's channel pair -------------------------------------------------------
@@ -90,12 +114,12 @@ __device__ __forceinline__ void sigmoid_pair(float gx, float ga, float& i, float
   }
 }
 
-// both gates of both channels
+// both gates of both channels; bx, ba: gate_bias_term of the two gates
 template <bool FAST>
-__device__ __forceinline__ void gates2(float2 gx, float2 ga, float2& i, float2& r) {
+__device__ __forceinline__ void gates2(float2 gx, float2 ga, float2 bx, float2 ba, float2& i, float2& r) {
   if (FAST) {
-    float2 tx = mul2(gx, f2(-kLog2e)), ta = mul2(ga, f2(-kLog2e));
-    tx.x = ex2_approx(tx.x);  // inputs were floored at -29 when loaded (SmemPair::ld_gate)
+    float2 tx = fma2(gx, f2(-kLog2e), bx), ta = fma2(ga, f2(-kLog2e), ba);
+    tx.x = ex2_approx(tx.x);  // at most 2^62: the inputs were floored when loaded (SmemPair::ld_gate)
     tx.y = ex2_approx(tx.y);
     ta.x = ex2_approx(ta.x);
     ta.y = ex2_approx(ta.y);
@@ -106,8 +130,8 @@ __device__ __forceinline__ void gates2(float2 gx, float2 ga, float2& i, float2& 
     i = mul2(v, w);
     r = mul2(u, w);
   } else {
-    sigmoid_pair<false>(gx.x, ga.x, i.x, r.x);
-    sigmoid_pair<false>(gx.y, ga.y, i.y, r.y);
+    sigmoid_pair<false>(gx.x + bx.x, ga.x + ba.x, i.x, r.x);
+    sigmoid_pair<false>(gx.y + bx.y, ga.y + ba.y, i.y, r.y);
   }
 }
 
@@ -136,10 +160,11 @@ __device__ __forceinline__ void fwd_coeffs(float x, float gx, float ga, float k,
 
 // (a, beta) of one row for the lane's channel pair
 template <bool FAST>
-__device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, float2 k, float2& a, float2& beta) {
+__device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, float2 bx, float2 ba, float2 k,
+                                            float2& a, float2& beta) {
   if (FAST) {
     float2 i, r;
-    gates2<true>(gx, ga, i, r);
+    gates2<true>(gx, ga, bx, ba, i, r);
     a = decay2<true>(k, r);
     const float2 v = fma2(neg2(a), a, f2(1.f));
     float2 m;
@@ -147,8 +172,8 @@ __device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, floa
     m.y = sqrt_approx(v.y);
     beta = mul2(mul2(x, i), m);
   } else {
-    fwd_coeffs<false>(x.x, gx.x, ga.x, k.x, a.x, beta.x);
-    fwd_coeffs<false>(x.y, gx.y, ga.y, k.y, a.y, beta.y);
+    fwd_coeffs<false>(x.x, gx.x + bx.x, ga.x + ba.x, k.x, a.x, beta.x);
+    fwd_coeffs<false>(x.y, gx.y + bx.y, ga.y + ba.y, k.y, a.y, beta.y);
   }
 }
 
@@ -201,8 +226,8 @@ struct Geo {
 template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
-                const float* __restrict__ lam, const float* __restrict__ h0, T* __restrict__ h,
-                int T_len, int D) {
+                const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
+                T* __restrict__ h, int T_len, int D) {
   using G = Geo<T, R, WARPS, LPR, 3>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -222,6 +247,11 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 
   const float2 lam2 = *reinterpret_cast<const float2*>(lam + ch);
   const float2 k2 = make_float2(gate_scale<FAST>(lam2.x), gate_scale<FAST>(lam2.y));
+  // gate biases [2, D]: row 0 for gx, row 1 for ga (zero when absent)
+  float2 bgx, bga;
+  uint32_t fgx, fga;
+  gate_bias_term<T, FAST>(gbias, 0, D, ch, bgx, fgx);
+  gate_bias_term<T, FAST>(gbias, 1, D, ch, bga, fga);
   if (threadIdx.x < LPR) {
     state[0][threadIdx.x] =
         h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch0 + 2 * threadIdx.x) : make_float2(0.f, 0.f);
@@ -288,8 +318,8 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     for (int r = 0; r < R; ++r) {
       if (FULL || t0 + r < T_len) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
-        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld_gate(row + G::IN_BYTES),
-                          SmemPair<T>::ld_gate(row + 2 * G::IN_BYTES), k2, a[r], be[r]);
+        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld_gate(row + G::IN_BYTES, fgx),
+                          SmemPair<T>::ld_gate(row + 2 * G::IN_BYTES, fga), bgx, bga, k2, a[r], be[r]);
       } else {  // past the end: identity step
         a[r] = f2(1.f);
         be[r] = f2(0.f);
@@ -331,9 +361,10 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
-                const float* __restrict__ lam, const float* __restrict__ h0, const T* __restrict__ h,
-                const T* __restrict__ go, T* __restrict__ dx, T* __restrict__ dgx, T* __restrict__ dga,
-                float* __restrict__ dlam_partial, float* __restrict__ dh0, int T_len, int D) {
+                const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
+                const T* __restrict__ h, const T* __restrict__ go, T* __restrict__ dx, T* __restrict__ dgx,
+                T* __restrict__ dga, float* __restrict__ dlam_partial, float* __restrict__ dgb_partial,
+                float* __restrict__ dh0, int T_len, int D, int B_total) {
   using G = Geo<T, R, WARPS, LPR, 5>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -357,6 +388,10 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   // factor that turns d(log a) into d(ga)/(r(1-r)):  C * softplus(lam), in natural-log units
   const float2 q2 = FAST ? make_float2(k2.x * (1.f / kLog2e), k2.y * (1.f / kLog2e)) : k2;
   const float2 h0v = h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch) : make_float2(0.f, 0.f);
+  float2 bgx, bga;
+  uint32_t fgx, fga;
+  gate_bias_term<T, FAST>(gbias, 0, D, ch, bgx, fgx);
+  gate_bias_term<T, FAST>(gbias, 1, D, ch, bga, fga);
   if (threadIdx.x < LPR) state[0][threadIdx.x] = make_float2(0.f, 0.f);  // c_T = 0
 
   static_assert((STAGES & (STAGES - 1)) == 0, "STAGES must be a power of two");
@@ -401,6 +436,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
   float2 acc = f2(0.f);  // sum over t of dlog_a * r  (times C*sigmoid(lam) at the end)
+  float2 acc_bx = f2(0.f), acc_ba = f2(0.f);  // sums over t of d gx, d ga: the gate-bias gradients
   T* dxp = dx + base + ch;
   T* dgxp = dgx + base + ch;
   T* dgap = dga + base + ch;
@@ -426,7 +462,8 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       if (FULL || tt - r >= 0) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
         gov = SmemPair<T>::ld(row + G::IN_BYTES);
-        gates2<FAST>(SmemPair<T>::ld_gate(row + 3 * G::IN_BYTES), SmemPair<T>::ld_gate(row), ig[r], rg[r]);
+        gates2<FAST>(SmemPair<T>::ld_gate(row + 3 * G::IN_BYTES, fgx), SmemPair<T>::ld_gate(row, fga), bgx, bga, ig[r],
+                     rg[r]);
         a[r] = decay2<FAST>(k2, rg[r]);
       } else {
         rg[r] = ig[r] = f2(0.f);
@@ -503,6 +540,8 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
         o_dgx = make_float2(dgxs[0], dgxs[1]);
         o_dga = make_float2(dgas[0], dgas[1]);
       }
+      acc_bx = add2(acc_bx, o_dgx);
+      acc_ba = add2(acc_ba, o_dga);
       const uint32_t o = (uint32_t)t * uD;
       P_::store(dxp + o, o_dx.x, o_dx.y);
       P_::store(dgxp + o, o_dgx.x, o_dgx.y);
@@ -536,21 +575,42 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       *reinterpret_cast<float2*>(dh0 + (size_t)b * D + ch0 + 2 * c2) = state[nsteps & 1][c2];
     }
   }
+  if (dgb_partial != nullptr) {  // gate-bias gradient partials [2][B][D], same fixed-order reduction
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __syncthreads();
+      red[slot][cl] = which ? acc_ba : acc_bx;
+      __syncthreads();
+      if (threadIdx.x < LPR) {
+        const int c2 = threadIdx.x;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < G::SLOTS; ++j) {
+          s0 += red[j][c2].x;
+          s1 += red[j][c2].y;
+        }
+        *reinterpret_cast<float2*>(dgb_partial + ((size_t)which * B_total + b) * D + ch0 + 2 * c2) = make_float2(s0, s1);
+      }
+    }
+  }
 }
 
-// dlam[d] = sum_b partial[b][d]   (scan_fused.py:424), fixed order => deterministic
-__global__ void scan_dlam_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dlam, int B, int D) {
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+// out[v][d] = sum_b partial[v][b][d] for v < nvec (v = 0: dlam, scan_fused.py:424; v = 1, 2: the gate
+// biases), fixed order => deterministic
+__global__ void scan_dlam_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dlam,
+                                        float* __restrict__ dgb, int B, int D, int nvec) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= nvec * D) return;
+  const int v = idx / D, d = idx - v * D;
   float s = 0.f;
-  for (int b = 0; b < B; ++b) s += partial[(size_t)b * D + d];
-  dlam[d] = s;
+  for (int b = 0; b < B; ++b) s += partial[((size_t)v * B + b) * D + d];
+  if (v == 0) dlam[d] = s; else dgb[(size_t)(v - 1) * D + d] = s;
 }
 
 // ---- launch ---------------------------------------------------------------------------------
 template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
-static int launch_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0, void* h,
-                      int B, int T_len, int D, cudaStream_t st) {
+static int launch_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                      const float* gbias, void* h, int B, int T_len, int D, cudaStream_t st) {
   using G = Geo<T, R, WARPS, LPR, 3>;
   auto kern = scan_fwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
@@ -559,14 +619,16 @@ static int launch_fwd(const void* x, const void* gx, const void* ga, const float
     return HAWK_ERR_LAUNCH;
   }
   kern<<<B * (D / G::CW), WARPS * 32, smem, st>>>(static_cast<const T*>(x), static_cast<const T*>(gx),
-                                                   static_cast<const T*>(ga), lam, h0, static_cast<T*>(h), T_len, D);
+                                                   static_cast<const T*>(ga), lam, h0, gbias, static_cast<T*>(h),
+                                                   T_len, D);
   return launch_status();
 }
 
 template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
 static int launch_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                      const void* h, const void* go, void* dx, void* dgx, void* dga, float* dlam, float* dh0,
-                      float* partial, int B, int T_len, int D, cudaStream_t st) {
+                      const float* gbias, const void* h, const void* go, void* dx, void* dgx, void* dga,
+                      float* dlam, float* dh0, float* dgbias, float* partial, int B, int T_len, int D,
+                      cudaStream_t st) {
   using G = Geo<T, R, WARPS, LPR, 5>;
   auto kern = scan_bwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
@@ -575,12 +637,13 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
     return HAWK_ERR_LAUNCH;
   }
   kern<<<B * (D / G::CW), WARPS * 32, smem, st>>>(
-      static_cast<const T*>(x), static_cast<const T*>(gx), static_cast<const T*>(ga), lam, h0,
+      static_cast<const T*>(x), static_cast<const T*>(gx), static_cast<const T*>(ga), lam, h0, gbias,
       static_cast<const T*>(h), static_cast<const T*>(go), static_cast<T*>(dx), static_cast<T*>(dgx),
-      static_cast<T*>(dga), partial, dh0, T_len, D);
+      static_cast<T*>(dga), partial, dgbias ? partial + (size_t)B * D : nullptr, dh0, T_len, D, B);
   int rc = launch_status();
   if (rc != HAWK_OK) return rc;
-  scan_dlam_reduce_kernel<<<(D + 255) / 256, 256, 0, st>>>(partial, dlam, B, D);
+  const int nvec = dgbias ? 3 : 1;
+  scan_dlam_reduce_kernel<<<(nvec * D + 255) / 256, 256, 0, st>>>(partial, dlam, dgbias, B, D, nvec);
   return launch_status();
 }
 
@@ -610,17 +673,17 @@ static int check_scan_common(int B, int T, int D, int dtype) {
 using namespace hawk;
 
 extern "C" int hawk_scan_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                             void* h, int B, int T, int D, int dtype, void* stream) {
+                             const float* gate_bias, void* h, int B, int T, int D, int dtype, void* stream) {
   HAWK_REQUIRE(x && gx && ga && lam && h, HAWK_ERR_NULL);
   int rc = check_scan_common(B, T, D, dtype);
   if (rc != HAWK_OK) return rc;
   HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(lam, 8) &&
-                   aligned(h0, 8),
+                   aligned(h0, 8) && aligned(gate_bias, 8),
                HAWK_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   using bf = __nv_bfloat16;
 #define HAWK_FWD(TT, R, W, LPR, S, MINB, FAST) \
-  return launch_fwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, h, B, T, D, st)
+  return launch_fwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, gate_bias, h, B, T, D, st)
   const int cfg = pick_cfg(B, D, false);
   if (dtype == HAWK_BF16) {
     switch (cfg) {
@@ -643,27 +706,29 @@ extern "C" int hawk_scan_fwd(const void* x, const void* gx, const void* ga, cons
 
 extern "C" size_t hawk_scan_bwd_workspace_bytes(int B, int D) {
   if (B < 1 || D < 1) return 0;
-  return (size_t)B * (size_t)D * sizeof(float);
+  return 3 * (size_t)B * (size_t)D * sizeof(float);  // Lambda and the two gate-bias partial planes
 }
 
 extern "C" int hawk_scan_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                             const void* h, const void* go, void* dx, void* dgx, void* dga, float* dlam,
-                             float* dh0, void* workspace, size_t workspace_bytes, int B, int T, int D,
-                             int dtype, void* stream) {
+                             const float* gate_bias, const void* h, const void* go, void* dx, void* dgx,
+                             void* dga, float* dlam, float* dh0, float* dgate_bias, void* workspace,
+                             size_t workspace_bytes, int B, int T, int D, int dtype, void* stream) {
   HAWK_REQUIRE(x && gx && ga && lam && h && go && dx && dgx && dga && dlam, HAWK_ERR_NULL);
   int rc = check_scan_common(B, T, D, dtype);
   if (rc != HAWK_OK) return rc;
-  HAWK_REQUIRE(workspace && workspace_bytes >= hawk_scan_bwd_workspace_bytes(B, D), HAWK_ERR_WORKSPACE);
+  // one [B,D] fp32 plane of partials for Lambda, two more when the gate-bias gradients are wanted
+  HAWK_REQUIRE(workspace && workspace_bytes >= (dgate_bias ? 3 : 1) * (size_t)B * (size_t)D * sizeof(float),
+               HAWK_ERR_WORKSPACE);
   HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(go, 16) &&
                    aligned(dx, 8) && aligned(dgx, 8) && aligned(dga, 8) && aligned(lam, 8) && aligned(h0, 8) &&
-                   aligned(dh0, 8) && aligned(workspace, 16),
+                   aligned(dh0, 8) && aligned(gate_bias, 8) && aligned(dgate_bias, 4) && aligned(workspace, 16),
                HAWK_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(workspace);
   using bf = __nv_bfloat16;
 #define HAWK_BWD(TT, R, W, LPR, S, MINB, FAST)                                                                  \
-  return launch_bwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, h, go, dx, dgx, dga, dlam, dh0, partial, B, \
-                                                  T, D, st)
+  return launch_bwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, gate_bias, h, go, dx, dgx, dga, dlam, dh0, \
+                                                  dgate_bias, partial, B, T, D, st)
   const int cfg = pick_cfg(B, D, true);
   if (dtype == HAWK_BF16) {
     switch (cfg) {
@@ -735,6 +800,7 @@ extern "C" int hawk_scan_bwd_noalloc(const void* x, const void* gx, const void* 
   float* scratch = nullptr;
   const int rc = hawk::noalloc_scratch_for_current_device(&scratch);
   if (rc != HAWK_OK) return rc;
-  return hawk_scan_bwd(x, gx, ga, lam, h0, h, go, dx, dgx, dga, dlam, dh0, scratch,
-                       (size_t)hawk::kNoAllocMaxBD * sizeof(float), B, T, D, dtype, stream);
+  return hawk_scan_bwd(x, gx, ga, lam, h0, /*gate_bias=*/nullptr, h, go, dx, dgx, dga, dlam, dh0,
+                       /*dgate_bias=*/nullptr, scratch, (size_t)hawk::kNoAllocMaxBD * sizeof(float), B, T, D, dtype,
+                       stream);
 }

@@ -14,16 +14,16 @@ LIB_PATH = os.path.join(_HERE, "libhawk_b200.so")
 
 HAWK_F32 = 0
 HAWK_BF16 = 1
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _P = c_void_p
 # name -> (restype, argtypes); mirrors include/hawk_b200.h one to one
 SIGNATURES = {
     "hawk_version": (c_int, []),
     "hawk_strerror": (c_char_p, [c_int]),
-    "hawk_scan_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "hawk_scan_fwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
-    "hawk_scan_bwd": (c_int, [_P] * 13 + [c_size_t, c_int, c_int, c_int, c_int, _P]),
+    "hawk_scan_bwd": (c_int, [_P] * 15 + [c_size_t, c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_noalloc": (c_int, [_P] * 12 + [c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_fwd": (c_int, [_P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),

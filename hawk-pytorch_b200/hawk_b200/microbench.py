@@ -78,9 +78,10 @@ def main(argv=None):
         x, gx, ga, go = (torch.randn(a.B, a.T, a.D, generator=g, device=dev).to(dt) for _ in range(4))
         lam = ring_init_(torch.empty(a.D)).to(dev)
         n = a.B * a.T * a.D
-        h = ops.scan_fwd(x, gx, ga, lam, None)
-        tf = _time(lambda: ops.scan_fwd(x, gx, ga, lam, None), a.iters, a.warmup, flush)
-        tb = _time(lambda: ops.scan_bwd(x, gx, ga, lam, None, h, go), a.iters, a.warmup, flush)
+        gb = 0.1 * torch.randn(2, a.D, generator=g, device=dev)  # gate biases, as the model passes them
+        h = ops.scan_fwd(x, gx, ga, lam, None, gb)
+        tf = _time(lambda: ops.scan_fwd(x, gx, ga, lam, None, gb), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.scan_bwd(x, gx, ga, lam, None, gb, h, go), a.iters, a.warmup, flush)
         _emit("scan_fwd", tf, 4 * es * n, "GB/s", **shape)
         _emit("scan_bwd", tb, 8 * es * n, "GB/s", **shape)
         _emit("scan_fwd+bwd", tf + tb, 12 * es * n, "GB/s", **shape)

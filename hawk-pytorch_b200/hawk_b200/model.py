@@ -189,9 +189,11 @@ class Hawk(nn.Module):
 
         self.conv1d.out_dtype = xb.dtype  # store the conv result in the activation dtype
         xc = self.conv1d(xb)
-        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, self.rg_lru_input_gate.b,
-                                      self.rg_lru_a_gate.w, self.rg_lru_a_gate.b)
-        h = ops.fused_linear_scan(xc, gx, ga, self.rg_lru_a_param.float())
+        # the gate biases go to the scan kernel, which adds them for free and sums their gradients:
+        # the projections write bias-free outputs (no broadcast bias pass, no separate reductions)
+        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, None, self.rg_lru_a_gate.w, None)
+        gate_bias = torch.stack((self.rg_lru_input_gate.b.reshape(-1), self.rg_lru_a_gate.b.reshape(-1))).float()
+        h = ops.fused_linear_scan(xc, gx, ga, self.rg_lru_a_param.float(), gate_bias=gate_bias)
         cache = None
         if self.use_cache:
             assert layer_past is not None, "use_cache=True needs an RNNCache per layer"

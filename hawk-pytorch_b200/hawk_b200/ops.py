@@ -112,27 +112,32 @@ class _on:
 # ---------------------------------------------------------------------------------------------
 @torch.library.custom_op("hawk_b200::scan_fwd", mutates_args=())
 def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
-             h0: Optional[torch.Tensor] = None) -> torch.Tensor:
+             h0: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = _lib.load()
     B, T, D = x.shape
     x, gx, ga, lam = x.contiguous(), gx.contiguous(), ga.contiguous(), lam.contiguous()
     if h0 is not None:
         h0 = h0.contiguous()
+    if gate_bias is not None:
+        assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
+        gate_bias = gate_bias.contiguous()
     h = torch.empty_like(x)
     with _on(x, "scan_fwd", 1):
         _lib.check(lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
-                                     h.data_ptr(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd")
+                                     _ptr(gate_bias), h.data_ptr(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd")
     return h
 
 
 @scan_fwd.register_fake
-def _(x, gx, ga, lam, h0=None):
+def _(x, gx, ga, lam, h0=None, gate_bias=None):
     return torch.empty_like(x, memory_format=torch.contiguous_format)
 
 
 @torch.library.custom_op("hawk_b200::scan_bwd", mutates_args=())
 def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor, h0: Optional[torch.Tensor],
-             h: torch.Tensor, go: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+             gate_bias: Optional[torch.Tensor], h: torch.Tensor, go: torch.Tensor
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dx, dgx, dga, dlam, dh0, dgate_bias); dgate_bias is [2, D] (empty [0, D] without gate_bias)."""
     lib = _lib.load()
     B, T, D = x.shape
     x, gx, ga, lam, h, go = (t.contiguous() for t in (x, gx, ga, lam, h, go))
@@ -141,48 +146,56 @@ def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
     dx, dgx, dga = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
     dlam = torch.empty(D, dtype=torch.float32, device=x.device)
     dh0 = torch.empty(B, D, dtype=torch.float32, device=x.device)
-    ws_bytes = lib.hawk_scan_bwd_workspace_bytes(B, D)
+    dgb = torch.empty(2 if gate_bias is not None else 0, D, dtype=torch.float32, device=x.device)
+    ws_bytes = (3 if gate_bias is not None else 1) * B * D * 4
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     if h0 is not None:
         h0 = h0.contiguous()
+    if gate_bias is not None:
+        gate_bias = gate_bias.contiguous()
     with _on(x, "scan_bwd", 2):
         _lib.check(lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
-                                     h.data_ptr(), go.data_ptr(), dx.data_ptr(), dgx.data_ptr(), dga.data_ptr(),
-                                     dlam.data_ptr(), dh0.data_ptr(), ws.data_ptr(), ws_bytes, B, T, D, _dt(x),
-                                     _stream(x)), "hawk_scan_bwd")
-    return dx, dgx, dga, dlam, dh0
+                                     _ptr(gate_bias), h.data_ptr(), go.data_ptr(), dx.data_ptr(), dgx.data_ptr(),
+                                     dga.data_ptr(), dlam.data_ptr(), dh0.data_ptr(),
+                                     dgb.data_ptr() if gate_bias is not None else None, ws.data_ptr(), ws_bytes,
+                                     B, T, D, _dt(x), _stream(x)), "hawk_scan_bwd")
+    return dx, dgx, dga, dlam, dh0, dgb
 
 
 @scan_bwd.register_fake
-def _(x, gx, ga, lam, h0, h, go):
+def _(x, gx, ga, lam, h0, gate_bias, h, go):
     B, T, D = x.shape
     e = lambda: torch.empty_like(x, memory_format=torch.contiguous_format)
-    return e(), e(), e(), x.new_empty(D, dtype=torch.float32), x.new_empty(B, D, dtype=torch.float32)
+    return (e(), e(), e(), x.new_empty(D, dtype=torch.float32), x.new_empty(B, D, dtype=torch.float32),
+            x.new_empty(2 if gate_bias is not None else 0, D, dtype=torch.float32))
 
 
 def _scan_setup(ctx, inputs, output):
-    x, gx, ga, lam, h0 = inputs
-    ctx.save_for_backward(x, gx, ga, lam, h0, output)
+    x, gx, ga, lam, h0, gate_bias = inputs
+    ctx.save_for_backward(x, gx, ga, lam, h0, gate_bias, output)
     ctx.has_h0 = h0 is not None
+    ctx.has_bias = gate_bias is not None
 
 
 def _scan_backward(ctx, go):
-    x, gx, ga, lam, h0, h = ctx.saved_tensors
-    dx, dgx, dga, dlam, dh0 = scan_bwd(x, gx, ga, lam, h0, h, go)
-    return dx, dgx, dga, dlam, (dh0 if ctx.has_h0 else None)
+    x, gx, ga, lam, h0, gate_bias, h = ctx.saved_tensors
+    dx, dgx, dga, dlam, dh0, dgb = scan_bwd(x, gx, ga, lam, h0, gate_bias, h, go)
+    return dx, dgx, dga, dlam, (dh0 if ctx.has_h0 else None), (dgb if ctx.has_bias else None)
 
 
 scan_fwd.register_autograd(_scan_backward, setup_context=_scan_setup)
 
 
-def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None):
+def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None, gate_bias=None):
     """h = RG-LRU scan of (x, input-gate pre-activation, recurrence-gate pre-activation, Lambda).
 
     Drop-in for hawk/scan_fused.py:445.  As in the reference (custom_fwd(cast_inputs=bfloat16),
     scan_fused.py:428) the three activation tensors are taken in bf16 under CUDA autocast and in
     their own dtype otherwise, and h has that dtype.  Lambda and its gradient stay fp32 here (the
-    reference rounds Lambda to bf16 under autocast).  `h0` ([B,D], optional) is an extension;
-    the default reproduces the reference's zero initial state.
+    reference rounds Lambda to bf16 under autocast).  Two extensions, both off by default: `h0`
+    ([B,D]) is the initial state (the reference's is zero); `gate_bias` ([2,D] fp32: input-gate row,
+    recurrence-gate row) is added to the gate pre-activations inside the kernel, so that the caller
+    can pass bias-free gate projections and gets the bias gradients from the scan's backward.
     """
     if torch.is_autocast_enabled("cuda"):
         dt = torch.bfloat16
@@ -192,7 +205,9 @@ def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None):
     lam = a_param if a_param.dtype == torch.float32 else a_param.float()
     if h0 is not None and h0.dtype != torch.float32:
         h0 = h0.float()
-    return scan_fwd(x, x_rg_lru, a_rg_lru, lam, h0)
+    if gate_bias is not None and gate_bias.dtype != torch.float32:
+        gate_bias = gate_bias.float()
+    return scan_fwd(x, x_rg_lru, a_rg_lru, lam, h0, gate_bias)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -640,10 +655,15 @@ class _BlockDiagGates(torch.autograd.Function):
             xb = x2.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
             out = torch.empty(2, M, R, dtype=dt, device=x.device)
             wxc, wac = wx.to(dt), wa.to(dt)
-            torch.baddbmm(bx.to(dt).unsqueeze(1), xb, wxc, out=out[0].view(M, nb, bw).transpose(0, 1))
-            torch.baddbmm(ba.to(dt).unsqueeze(1), xb, wac, out=out[1].view(M, nb, bw).transpose(0, 1))
+            ox, oa = (out[j].view(M, nb, bw).transpose(0, 1) for j in (0, 1))
+            if bx is None:  # the caller adds the biases downstream (inside the scan kernel)
+                torch.bmm(xb, wxc, out=ox)
+                torch.bmm(xb, wac, out=oa)
+            else:
+                torch.baddbmm(bx.to(dt).unsqueeze(1), xb, wxc, out=ox)
+                torch.baddbmm(ba.to(dt).unsqueeze(1), xb, wac, out=oa)
         ctx.save_for_backward(x2, wxc, wac)
-        ctx.meta = (shape, nb, bw, wx.dtype, bx.dtype)
+        ctx.meta = (shape, nb, bw, wx.dtype, None if bx is None else bx.dtype)
         return out[0].view(shape), out[1].view(shape)
 
     @staticmethod
@@ -660,17 +680,22 @@ class _BlockDiagGates(torch.autograd.Function):
             xbT = x2.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
             dwx = torch.bmm(xbT, gxb)
             dwa = torch.bmm(xbT, gab)
-            dbx = dgx2.view(M, nb, bw).sum(dim=0, dtype=torch.float32)
-            dba = dga2.view(M, nb, bw).sum(dim=0, dtype=torch.float32)
+            dbx = dba = None
+            if bdt is not None:
+                dbx = dgx2.view(M, nb, bw).sum(dim=0, dtype=torch.float32).to(bdt)
+                dba = dga2.view(M, nb, bw).sum(dim=0, dtype=torch.float32).to(bdt)
             dx = torch.empty(M, R, dtype=dt, device=x2.device)
             dxb = dx.view(M, nb, bw).transpose(0, 1)
             torch.bmm(gxb, wxc.transpose(1, 2), out=dxb)
             torch.baddbmm(dxb, gab, wac.transpose(1, 2), out=dxb)
-        return dx.view(shape), dwx.to(wdt), dbx.to(bdt), dwa.to(wdt), dba.to(bdt)
+        return dx.view(shape), dwx.to(wdt), dbx, dwa.to(wdt), dba
 
 
 def block_diag_gates(x, wx, bx, wa, ba):
-    """(input-gate, recurrence-gate) pre-activations of the RG-LRU from the conv output x [..., R]."""
+    """(input-gate, recurrence-gate) pre-activations of the RG-LRU from the conv output x [..., R].
+    With bx = ba = None the projections are returned without their biases, for a caller that hands
+    the biases to `fused_linear_scan(..., gate_bias=)`."""
+    assert (bx is None) == (ba is None)
     return _BlockDiagGates.apply(x, wx, bx, wa, ba)
 
 

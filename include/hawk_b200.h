@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define HAWK_B200_ABI_VERSION 1
+#define HAWK_B200_ABI_VERSION 2
 
 typedef enum hawk_dtype { HAWK_F32 = 0, HAWK_BF16 = 1 } hawk_dtype;
 
@@ -62,20 +62,28 @@ const char* hawk_strerror(int status);
  * D must be a multiple of 64 (as the reference asserts, scan_fused.py:333); T >= 1.
  * h0 / dh0: optional [B,D] fp32 (no counterpart in the reference, whose initial state is
  * fixed at zero, scan_fused.py:77-79); pass NULL for the reference behaviour.
+ * gate_bias / dgate_bias: optional [2,D] fp32, row 0 for gx and row 1 for ga.  With gate_bias the
+ * gates are sigmoid(gx + gate_bias[0]) and sigmoid(ga + gate_bias[1]): the bias add of the
+ * reference's block-diagonal gate projections (BlockDiagonalLinear, hawk/hawk.py:41-45, applied at
+ * :128-129) done inside the scan, with the sum rounded to `dtype` as the reference's add is.  The
+ * caller then passes the bias-free projections as gx, ga.  dgate_bias receives the sums of dgx and
+ * dga over batch and time (what autograd's bias gradient computes), in fp32, in a fixed order.
+ * Pass NULL for the reference's scan signature.
  * The backward reads the forward OUTPUT h (as stored) for h_{t-1}, like the reference.
- * Workspace (backward only): hawk_scan_bwd_workspace_bytes(B, D) bytes, 16-byte aligned.
+ * Workspace (backward only): 16-byte aligned; B*D*4 bytes, three times that when dgate_bias is
+ * given; hawk_scan_bwd_workspace_bytes(B, D) returns the larger figure.
  * ---------------------------------------------------------------------------------------- */
 int hawk_scan_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                  void* h, int B, int T, int D, int dtype, void* stream);
+                  const float* gate_bias, void* h, int B, int T, int D, int dtype, void* stream);
 size_t hawk_scan_bwd_workspace_bytes(int B, int D);
 int hawk_scan_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                  const void* h, const void* go, void* dx, void* dgx, void* dga, float* dlam,
-                  float* dh0, void* workspace, size_t workspace_bytes, int B, int T, int D,
-                  int dtype, void* stream);
+                  const float* gate_bias, const void* h, const void* go, void* dx, void* dgx, void* dga,
+                  float* dlam, float* dh0, float* dgate_bias, void* workspace, size_t workspace_bytes,
+                  int B, int T, int D, int dtype, void* stream);
 
 /* hawk_scan_bwd for hosts that cannot allocate device memory (no counterpart in the reference, which
  * allocates its scratch with torch.empty on every call, hawk/scan_fused.py:378).  Same arguments and
- * results as hawk_scan_bwd but no workspace: the [B,D] fp32 scratch is a fixed 1 MiB array inside the
+ * results as hawk_scan_bwd without gate biases, but no workspace: the [B,D] fp32 scratch is a fixed 1 MiB array inside the
  * library (per GPU, kept until exit), so B * D <= 262144 or HAWK_ERR_TOO_LARGE.  Calls nothing that
  * allocates.  The first call on each device looks the array's device address up (make it outside a
  * stream capture).  All calls on a device share the array: calls overlapping on the GPU race. */

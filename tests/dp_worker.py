@@ -15,17 +15,33 @@ from hawk_b200 import train  # noqa: E402
 from oracle import model as omodel  # noqa: E402
 
 
-def patch_ops():
-    M.ops.fused_linear_scan = lambda x, gx, ga, lam, h0=None: omodel.scan(x, gx, ga, lam)
-    M.ops.fused_cross_entropy = lambda w, a, l: F.cross_entropy(F.linear(a, w), l)
-    M.ops.Conv1D.forward = lambda self, x: omodel.conv1d(x, self.w, self.b)
-    M.ops.rms_norm = lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w)
-    M.ops.add_rms_norm = lambda r, d, w, eps=1e-6, out_dtype=None: (
-        (r, omodel.rms_norm(r, w)) if d is None else (r + d, omodel.rms_norm(r + d, w)))
-    M.ops.geglu = lambda gu: F.gelu(gu.chunk(2, -1)[0]) * gu.chunk(2, -1)[1]
-    M.ops.gelu_mul = lambda a, b: F.gelu(a) * b
-    M.ops.block_diag_gates = lambda x, wx, bx, wa, ba: (omodel.block_diag_linear(x, wx, bx),
-                                                        omodel.block_diag_linear(x, wa, ba))
+def _scan_with_bias(x, gx, ga, lam, h0=None, gate_bias=None):
+    """The scan's gate_bias is the broadcast bias add of the gate projections moved inside it."""
+    if gate_bias is not None:
+        gx, ga = gx + gate_bias[0], ga + gate_bias[1]
+    return omodel.scan(x, gx, ga, lam)
+
+
+# oracle statements standing in for the kernels (the product has no CPU path; only tests do this)
+SUBSTITUTES = {
+    "fused_linear_scan": _scan_with_bias,
+    "fused_cross_entropy": lambda w, a, l: F.cross_entropy(F.linear(a, w), l),
+    "rms_norm": lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w),
+    "add_rms_norm": lambda r, d, w, eps=1e-6, out_dtype=None: (
+        (r, omodel.rms_norm(r, w)) if d is None else (r + d, omodel.rms_norm(r + d, w))),
+    "geglu": lambda gu: F.gelu(gu.chunk(2, -1)[0]) * gu.chunk(2, -1)[1],
+    "gelu_mul": lambda a, b: F.gelu(a) * b,
+    "block_diag_gates": lambda x, wx, bx, wa, ba: (omodel.block_diag_linear(x, wx, 0.0 if bx is None else bx),
+                                                   omodel.block_diag_linear(x, wa, 0.0 if ba is None else ba)),
+}
+CONV_FORWARD = lambda self, x: omodel.conv1d(x, self.w, self.b)  # noqa: E731
+
+
+def patch_ops(setattr_=setattr):
+    """In a worker process: plain setattr.  Inside pytest: pass monkeypatch.setattr so it is undone."""
+    for name, fn in SUBSTITUTES.items():
+        setattr_(M.ops, name, fn)
+    setattr_(M.ops.Conv1D, "forward", CONV_FORWARD)
 
 
 def make_trainer(world):

@@ -38,14 +38,19 @@ def test_strerror_is_total():
 def test_scan_argument_validation_needs_no_gpu():
     lib = L.load()
     p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
-    assert lib.hawk_scan_fwd(None, p, p, p, None, p, 1, 8, 64, L.HAWK_BF16, None) == -1      # NULL
-    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 8, 96, L.HAWK_BF16, None) == -2         # D % 64
-    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 0, 64, L.HAWK_BF16, None) == -2         # T < 1
-    assert lib.hawk_scan_fwd(p, p, p, p, None, p, 1, 8, 64, 7, None) == -3                   # dtype
-    assert lib.hawk_scan_fwd(ctypes.c_void_p(4098), p, p, p, None, p, 1, 8, 64, L.HAWK_BF16, None) == -4
-    assert lib.hawk_scan_bwd_workspace_bytes(8, 2048) == 8 * 2048 * 4
-    args = [p] * 4 + [None] + [p] * 6 + [None]
+    assert lib.hawk_scan_fwd(None, p, p, p, None, None, p, 1, 8, 64, L.HAWK_BF16, None) == -1      # NULL
+    assert lib.hawk_scan_fwd(p, p, p, p, None, None, p, 1, 8, 96, L.HAWK_BF16, None) == -2         # D % 64
+    assert lib.hawk_scan_fwd(p, p, p, p, None, None, p, 1, 0, 64, L.HAWK_BF16, None) == -2         # T < 1
+    assert lib.hawk_scan_fwd(p, p, p, p, None, None, p, 1, 8, 64, 7, None) == -3                   # dtype
+    assert lib.hawk_scan_fwd(ctypes.c_void_p(4098), p, p, p, None, None, p, 1, 8, 64, L.HAWK_BF16, None) == -4
+    assert lib.hawk_scan_fwd(p, p, p, p, None, ctypes.c_void_p(4100), p, 1, 8, 64, L.HAWK_BF16, None) == -4  # gate_bias
+    assert lib.hawk_scan_bwd_workspace_bytes(8, 2048) == 3 * 8 * 2048 * 4
+    # x gx ga lam | h0 gate_bias | h go dx dgx dga dlam | dh0 dgate_bias
+    args = [p] * 4 + [None, None] + [p] * 6 + [None, None]
     assert lib.hawk_scan_bwd(*args, p, 16, 8, 16, 2048, L.HAWK_BF16, None) == -5             # workspace too small
+    one_plane = 8 * 2048 * 4  # enough without the gate-bias gradients, too small with them
+    args = [p] * 4 + [None, p] + [p] * 6 + [None, p]
+    assert lib.hawk_scan_bwd(*args, p, one_plane, 8, 16, 2048, L.HAWK_BF16, None) == -5
 
 
 def test_conv_argument_validation_needs_no_gpu():

@@ -37,21 +37,8 @@ def test_two_ranks_match_single_process(tmp_path, monkeypatch):
     for k in r0["params"]:
         assert torch.equal(r0["params"][k], r1["params"][k]), k  # replicas stay bit-identical
 
-    import torch.nn.functional as F
     import dp_worker as W
-    import hawk_b200.model as M
-    from oracle import model as omodel
-    # the same substitution the workers make, undone by monkeypatch at the end of this test
-    monkeypatch.setattr(M.ops, "fused_linear_scan", lambda x, gx, ga, lam, h0=None: omodel.scan(x, gx, ga, lam))
-    monkeypatch.setattr(M.ops, "fused_cross_entropy", lambda w, a, l: F.cross_entropy(F.linear(a, w), l))
-    monkeypatch.setattr(M.ops.Conv1D, "forward", lambda self, x: omodel.conv1d(x, self.w, self.b))
-    monkeypatch.setattr(M.ops, "rms_norm", lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w))
-    monkeypatch.setattr(M.ops, "add_rms_norm", lambda r, d, w, eps=1e-6, out_dtype=None: (
-        (r, omodel.rms_norm(r, w)) if d is None else (r + d, omodel.rms_norm(r + d, w))))
-    monkeypatch.setattr(M.ops, "geglu", lambda gu: F.gelu(gu.chunk(2, -1)[0]) * gu.chunk(2, -1)[1])
-    monkeypatch.setattr(M.ops, "gelu_mul", lambda a, b: F.gelu(a) * b)
-    monkeypatch.setattr(M.ops, "block_diag_gates", lambda x, wx, bx, wa, ba: (
-        omodel.block_diag_linear(x, wx, bx), omodel.block_diag_linear(x, wa, ba)))
+    W.patch_ops(monkeypatch.setattr)  # the same substitution the workers make, undone after this test
     tr = W.make_trainer(1)
     single = [float(tr.step(W.data(s))) for s in range(3)]
     # the global loss is the mean of the two rank losses (equal token counts per rank)

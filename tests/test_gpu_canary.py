@@ -40,18 +40,22 @@ def test_scan_writes_stay_in_bounds(dtype, B, T, D):
     lam = torch.rand(D, device="cuda") * 4 - 6
     h, dx, dgx, dga = (Guarded((B, T, D), dtype) for _ in range(4))
     dlam, dh0 = Guarded((D,), torch.float32), Guarded((B, D), torch.float32)
+    gb = Guarded((2, D), torch.float32, torch.randn(2, D, generator=g, device="cuda"))
+    dgb = Guarded((2, D), torch.float32)
     ws_bytes = lib.hawk_scan_bwd_workspace_bytes(B, D)
     ws = Guarded((ws_bytes,), torch.uint8)
     st = torch.cuda.current_stream().cuda_stream
-    assert lib.hawk_scan_fwd(x.t.data_ptr(), gx.t.data_ptr(), ga.t.data_ptr(), lam.data_ptr(), None, h.t.data_ptr(),
+    assert lib.hawk_scan_fwd(x.t.data_ptr(), gx.t.data_ptr(), ga.t.data_ptr(), lam.data_ptr(), None, gb.t.data_ptr(),
+                             h.t.data_ptr(), B, T, D, code, st) == 0
+    assert lib.hawk_scan_bwd(x.t.data_ptr(), gx.t.data_ptr(), ga.t.data_ptr(), lam.data_ptr(), None, gb.t.data_ptr(),
+                             h.t.data_ptr(), go.t.data_ptr(), dx.t.data_ptr(), dgx.t.data_ptr(), dga.t.data_ptr(),
+                             dlam.t.data_ptr(), dh0.t.data_ptr(), dgb.t.data_ptr(), ws.t.data_ptr(), ws_bytes,
                              B, T, D, code, st) == 0
-    assert lib.hawk_scan_bwd(x.t.data_ptr(), gx.t.data_ptr(), ga.t.data_ptr(), lam.data_ptr(), None, h.t.data_ptr(),
-                             go.t.data_ptr(), dx.t.data_ptr(), dgx.t.data_ptr(), dga.t.data_ptr(), dlam.t.data_ptr(),
-                             dh0.t.data_ptr(), ws.t.data_ptr(), ws_bytes, B, T, D, code, st) == 0
     torch.cuda.synchronize()
-    for name, gd in dict(x=x, gx=gx, ga=ga, go=go, h=h, dx=dx, dgx=dgx, dga=dga, dlam=dlam, dh0=dh0, ws=ws).items():
+    for name, gd in dict(x=x, gx=gx, ga=ga, go=go, h=h, dx=dx, dgx=dgx, dga=dga, dlam=dlam, dh0=dh0, gb=gb, dgb=dgb,
+                         ws=ws).items():
         assert gd.intact(), name
-    for gd in (h, dx, dgx, dga, dlam, dh0):  # and every element inside was written
+    for gd in (h, dx, dgx, dga, dlam, dh0, dgb):  # and every element inside was written
         assert bool((gd.t.float() != 1024.0).all()) and bool(torch.isfinite(gd.t.float()).all())
 
 

@@ -151,6 +151,35 @@ def test_scan_noncontiguous_inputs_and_initial_state():
     _check(got, (h.detach(),) + grads, FP32_TOL, names=("h", "dx", "dgx", "dga", "dlam", "dh0"))
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL)])
+@pytest.mark.parametrize("B,T,D", [(1, 1, 64), (2, 33, 64), (3, 257, 192), (2, 2048, 512), (8, 300, 2048)])
+def test_scan_gate_bias_equals_bias_added_outside(B, T, D, dtype, tol):
+    """gate_bias=[bx; ba] inside the kernel == the oracle run on (gx + bx, ga + ba), which is what the
+    reference's block-diagonal projections hand its scan (hawk/hawk.py:128-129); the bias gradients
+    are the sums of d gx, d ga over batch and time (autograd of the broadcast add)."""
+    from hawk_b200 import fused_linear_scan
+    x, gx, ga, go, lam = _inputs(B, T, D, seed=31 + B + T + D, dtype=dtype)
+    g = torch.Generator().manual_seed(5)
+    gb = torch.randn(2, D, generator=g)
+    gb[0, ::7] = -40.0   # far below the kernel's internal floor: the gate is 0 either way
+    gb[1, 3::11] = 25.0  # saturated recurrence gate
+    dev = "cuda:0"
+    xs = [t.to(dev, dtype).requires_grad_(True) for t in (x, gx, ga)]
+    lam_d = lam.to(dev).requires_grad_(True)
+    gb_d = gb.to(dev).requires_grad_(True)
+    h = fused_linear_scan(*xs, lam_d, gate_bias=gb_d)
+    h.backward(go.to(dev, dtype))
+    got = [t.float().cpu() for t in (h.detach(), xs[0].grad, xs[1].grad, xs[2].grad, lam_d.grad, gb_d.grad)]
+    gxb, gab = gx + gb[0], ga + gb[1]
+    wh, wdx, wdgx, wdga, wdlam = _oracle(x, gxb, gab, go, lam, got[0])
+    want = (wh, wdx, wdgx, wdga, wdlam, torch.stack((wdgx.sum((0, 1)), wdga.sum((0, 1)))))
+    _check(got, want, tol, names=("h", "dx", "dgx", "dga", "dlam", "dgate_bias"))
+    # the bias gradient is the fixed-order sum of the gate gradients the kernel itself stored
+    if dtype == torch.float32:
+        own = torch.stack((got[2].double().sum((0, 1)), got[3].double().sum((0, 1)))).float()
+        assert rel_l2(got[5], own) <= 1e-5
+
+
 def test_scan_is_deterministic():
     x, gx, ga, go, lam = _inputs(4, 300, 256, seed=21, dtype=torch.bfloat16)
     a = _run_gpu(x, gx, ga, go, lam, torch.bfloat16)

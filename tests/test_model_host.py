@@ -25,16 +25,8 @@ def _cfg(g):
 @pytest.fixture
 def oracle_ops(monkeypatch):
     """The product has no CPU path; here the test itself substitutes oracle statements for the kernels."""
-    monkeypatch.setattr(M.ops, "fused_linear_scan", lambda x, gx, ga, lam, h0=None: omodel.scan(x, gx, ga, lam))
-    monkeypatch.setattr(M.ops, "fused_cross_entropy", lambda w, a, l: F.cross_entropy(F.linear(a, w), l))
-    monkeypatch.setattr(M.ops.Conv1D, "forward", lambda self, x: omodel.conv1d(x, self.w, self.b))
-    monkeypatch.setattr(M.ops, "rms_norm", lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w))
-    monkeypatch.setattr(M.ops, "add_rms_norm", lambda r, d, w, eps=1e-6, out_dtype=None: (
-        (r, omodel.rms_norm(r, w)) if d is None else (r + d, omodel.rms_norm(r + d, w))))
-    monkeypatch.setattr(M.ops, "geglu", lambda gu: F.gelu(gu.chunk(2, -1)[0]) * gu.chunk(2, -1)[1])
-    monkeypatch.setattr(M.ops, "gelu_mul", lambda a, b: F.gelu(a) * b)
-    monkeypatch.setattr(M.ops, "block_diag_gates", lambda x, wx, bx, wa, ba: (
-        omodel.block_diag_linear(x, wx, bx), omodel.block_diag_linear(x, wa, ba)))
+    import dp_worker
+    dp_worker.patch_ops(monkeypatch.setattr)
 
 
 def test_state_dict_contract():

@@ -22,8 +22,8 @@ def _both(lib, B, T, D, dtype, seed):
     code = 1 if dtype == torch.bfloat16 else 0
     stream = torch.cuda.current_stream().cuda_stream
     h = torch.empty_like(x)
-    assert lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None, h.data_ptr(),
-                             B, T, D, code, stream) == 0
+    assert lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None, None,
+                             h.data_ptr(), B, T, D, code, stream) == 0
 
     def outs():
         return [torch.empty_like(x) for _ in range(3)] + [torch.empty(D, device="cuda"), torch.empty(B, D, device="cuda")]
@@ -31,8 +31,8 @@ def _both(lib, B, T, D, dtype, seed):
     ref = outs()
     ws_bytes = lib.hawk_scan_bwd_workspace_bytes(B, D)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
-    rc = lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None, h.data_ptr(),
-                           go.data_ptr(), *[t.data_ptr() for t in ref], ws.data_ptr(), ws_bytes, B, T, D, code, stream)
+    rc = lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None, None, h.data_ptr(),
+                           go.data_ptr(), *[t.data_ptr() for t in ref], None, ws.data_ptr(), ws_bytes, B, T, D, code, stream)
     assert rc == 0
     got = outs()  # the caller still provides inputs and outputs; only the scratch is built in
     rc = lib.hawk_scan_bwd_noalloc(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None, h.data_ptr(),
