@@ -221,12 +221,106 @@ rms_norm_bwd_kernel(const TY* __restrict__ dy, const TX* __restrict__ x, const f
   }
 }
 
-__global__ void rows_sum_kernel(const float* __restrict__ partial, float* __restrict__ out, int rows, int H) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= H) return;
+// The same backward for H = 512 * NCH (NCH = 1, 2, 4, 8), one row per 128 threads, the row held in
+// registers between the dot product and the update: every input byte is loaded exactly once, all of a
+// row's loads (x, dy and the residual gradient: 10 x 16 bytes per thread at H = 2048) are in flight
+// together, and w is loaded once per thread because a thread keeps its columns for every row.  A CTA is two
+// independent row groups; a group's four warps meet once per row at a named barrier to sum the dot
+// product (double-buffered partials, so one barrier per row suffices).  dw partials: per-thread
+// column sums, the two groups added in shared memory, one partial row per CTA.
+template <typename TX, typename TY, int NCH>
+__global__ void __launch_bounds__(256, (NCH >= 8 ? 1 : 2))
+rms_norm_bwd_rows_kernel(const TY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                         const float* __restrict__ rstd, const TX* __restrict__ gres, TX* __restrict__ dx,
+                         TY* __restrict__ ddelta, float* __restrict__ dw_partial, int64_t M) {
+  constexpr int VEC = 4, TPR = 128, H = NCH * TPR * VEC;
+  __shared__ float part[2][2][4];         // [group][parity][warp of the group]
+  __shared__ float other[TPR * NCH * VEC];  // group 1's column sums
+  const int grp = threadIdx.x >> 7, t = threadIdx.x & (TPR - 1), lane = threadIdx.x & 31, wig = t >> 5;
+  float wv[NCH][VEC], acc[NCH][VEC];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    VecIO<float, VEC>::load(w + (c * TPR + t) * VEC, wv[c]);
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[c][q] = 0.f;
+  }
+  int par = 0;
+  for (int64_t m = (int64_t)blockIdx.x * 2 + grp; m < M; m += (int64_t)gridDim.x * 2) {
+    const int64_t row = m * H;
+    float xv[NCH][VEC], gv[NCH][VEC], rv[NCH][VEC];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) VecIO<TX, VEC>::load(x + row + (c * TPR + t) * VEC, xv[c]);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) VecIO<TY, VEC>::load(dy + row + (c * TPR + t) * VEC, gv[c]);
+    if (gres != nullptr) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) VecIO<TX, VEC>::load(gres + row + (c * TPR + t) * VEC, rv[c]);
+    }
+    const float inv = rstd[m];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        xv[c][q] *= inv;                                  // xhat
+        acc[c][q] = fmaf(gv[c][q], xv[c][q], acc[c][q]);  // dw += dy * xhat
+        gv[c][q] *= wv[c][q];                             // g = dy * w
+        dot = fmaf(gv[c][q], xv[c][q], dot);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) part[grp][par][wig] = dot;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(TPR) : "memory");
+    const float cmean = (((part[grp][par][0] + part[grp][par][1]) + part[grp][par][2]) + part[grp][par][3]) / (float)H;
+    par ^= 1;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float o[VEC];
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        o[q] = inv * (gv[c][q] - xv[c][q] * cmean);
+        if (gres != nullptr) o[q] += rv[c][q];  // gradient arriving at the summed residual from everything after it
+      }
+      VecIO<TX, VEC>::store(dx + row + (c * TPR + t) * VEC, o);
+      if (ddelta != nullptr) VecIO<TY, VEC>::store(ddelta + row + (c * TPR + t) * VEC, o);  // same value, delta's dtype
+    }
+  }
+  if (grp == 1) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) other[(c * TPR + t) * VEC + q] = acc[c][q];
+  }
+  __syncthreads();
+  if (grp == 0) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float o[VEC];
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) o[q] = acc[c][q] + other[(c * TPR + t) * VEC + q];
+      VecIO<float, VEC>::store(dw_partial + (int64_t)blockIdx.x * H + (c * TPR + t) * VEC, o);
+    }
+  }
+}
+
+// out[j] = sum_r partial[r][j] in a fixed order: 8 row slices per column summed by 8 threads, then
+// combined in shared memory
+__global__ void __launch_bounds__(256) rows_sum_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                       int rows, int H) {
+  __shared__ float sl[8][32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[(int64_t)r * H + j];
-  out[j] = s;
+  if (j < H)
+    for (int r = ty; r < rows; r += 8) s += partial[(int64_t)r * H + j];
+  sl[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < H) {
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += sl[k][tx];
+    out[j] = tot;
+  }
 }
 
 constexpr int kNormBwdCtas = 296;  // two per SM
@@ -330,6 +424,29 @@ static int norm_bwd_impl(const void* dy, const void* x, const float* w, const fl
                    aligned(gres, 16) && aligned(ddelta, 16),
                HAWK_ERR_ALIGN);
   float* partial = static_cast<float*>(workspace);
+  if (H % 512 == 0 && (H == 512 || H == 1024 || H == 2048 || H == 4096)) {  // rows-in-registers path
+#define HAWK_NORM_ROWS_N(TX, TY, N)                                                                                   \
+  rms_norm_bwd_rows_kernel<TX, TY, N><<<kNormBwdCtas, 256, 0, st>>>(                                                  \
+      static_cast<const TY*>(dy), static_cast<const TX*>(x), w, rstd, static_cast<const TX*>(gres),                   \
+      static_cast<TX*>(dx), static_cast<TY*>(ddelta), partial, M)
+#define HAWK_NORM_ROWS(TX, TY)                        \
+  do {                                                \
+    if (H == 512) HAWK_NORM_ROWS_N(TX, TY, 1);        \
+    else if (H == 1024) HAWK_NORM_ROWS_N(TX, TY, 2);  \
+    else if (H == 2048) HAWK_NORM_ROWS_N(TX, TY, 4);  \
+    else HAWK_NORM_ROWS_N(TX, TY, 8);                 \
+  } while (0)
+    if (x_dtype == HAWK_F32 && y_dtype == HAWK_BF16) HAWK_NORM_ROWS(float, bf);
+    else if (x_dtype == HAWK_F32) HAWK_NORM_ROWS(float, float);
+    else if (y_dtype == HAWK_BF16) HAWK_NORM_ROWS(bf, bf);
+    else HAWK_NORM_ROWS(bf, float);
+#undef HAWK_NORM_ROWS
+#undef HAWK_NORM_ROWS_N
+    int rc = launch_status();
+    if (rc != HAWK_OK) return rc;
+    rows_sum_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, dw, kNormBwdCtas, H);
+    return launch_status();
+  }
   const int smem = kNormBwdWarps * H * (int)sizeof(float);
   const int nch = (H + 127) / 128;
 #define HAWK_NORM_BWD_N(TX, TY, N)                                                                                  \
@@ -357,7 +474,7 @@ static int norm_bwd_impl(const void* dy, const void* x, const float* w, const fl
 #undef HAWK_NORM_BWD_N
   int rc = launch_status();
   if (rc != HAWK_OK) return rc;
-  rows_sum_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, kNormBwdCtas, H);
+  rows_sum_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, dw, kNormBwdCtas, H);
   return launch_status();
 }
 

@@ -86,7 +86,7 @@ def test_conv_writes_stay_in_bounds(dtype, B, T, D, W):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,J", [(1, 8), (5, 24), (1001, 64)])
+@pytest.mark.parametrize("M,J", [(1, 8), (5, 24), (1001, 64), (3, 256), (595, 128)])
 def test_glue_writes_stay_in_bounds(dtype, M, J):
     lib = _lib()
     code = 1 if dtype == torch.bfloat16 else 0

@@ -47,7 +47,7 @@ def test_geglu_and_strided_gelu_mul(dtype, M, J):
 
 @pytest.mark.parametrize("xdt,ydt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
                                      (torch.bfloat16, torch.bfloat16)])
-@pytest.mark.parametrize("M,H", [(1, 64), (33, 512), (1000, 2048), (257, 4096)])
+@pytest.mark.parametrize("M,H", [(1, 64), (33, 512), (2, 1024), (1000, 2048), (257, 4096), (1, 2048), (600, 384)])
 def test_rms_norm_matches_torch(xdt, ydt, M, H):
     from hawk_b200 import ops
     g = torch.Generator().manual_seed(M + H)
@@ -102,7 +102,7 @@ def test_block_diag_gates_match_einsum(dtype, nb, bw, lead):
 
 @pytest.mark.parametrize("xdt,ydt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
                                      (torch.bfloat16, torch.bfloat16)])
-@pytest.mark.parametrize("M,H", [(5, 64), (300, 2048)])
+@pytest.mark.parametrize("M,H", [(5, 64), (300, 2048), (1, 512), (700, 1024), (77, 4096), (593, 2048)])
 def test_add_rms_norm_matches_torch(xdt, ydt, M, H):
     """Fused residual add + norm: both outputs and all three gradients, with gradient arriving on the
     summed residual as well as on the norm output."""
