@@ -91,11 +91,6 @@ __device__ __forceinline__ void gate_bias_term(const float* __restrict__ gbias, 
 // ---- arithmetic on a lane's channel pair -------------------------------------------------------
 // sm_100 has packed fp32x2 add/mul/fma: one issue slot for both channels.  The kernels are issue
 // bound (about 40 instructions per element), so the FAST path does its FP32 work two at a time.
-__device__ __forceinline__ float2 f2(float v) { return make_float2(v, v); }
-__device__ __forceinline__ float2 neg2(float2 v) { return make_float2(-v.x, -v.y); }
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 
 // i = sigmoid(gx) and r = sigmoid(ga).  FAST shares one reciprocal between the two:
 // 1/(1+eg) = (1+ea) / ((1+eg)(1+ea)), three MUFU operations instead of four.  The exponent is

@@ -45,6 +45,29 @@ def test_geglu_and_strided_gelu_mul(dtype, M, J):
     assert rel_l2(b.grad.float().cpu(), r_b.grad) <= _tol(dtype)
 
 
+def test_bf16_gelu_is_the_erf_gelu_on_every_bf16_value():
+    """The bf16 kernels evaluate the exact GELU in logistic form (polynomial logit of the normal CDF);
+    on EVERY finite bf16 input the result is the erf GELU to within one bf16 rounding step, forward and
+    derivative, including the saturated tails and the largest magnitudes."""
+    from hawk_b200 import ops
+    bits = torch.arange(0, 65536, dtype=torch.int32).to(torch.int16)
+    a = bits.view(torch.bfloat16)
+    a = a[torch.isfinite(a)]
+    n = a.numel() // 8 * 8
+    a = a[:n].reshape(1, n).cuda()
+    one = torch.ones_like(a)
+    out = ops.gelu_mul_fwd(a, one)
+    da, db = ops.gelu_mul_bwd(one, a, one)
+    ad = a.double().cpu()
+    cdf = 0.5 * torch.erfc(-ad / 2 ** 0.5)
+    want = ad * cdf
+    dwant = cdf + ad * torch.exp(-0.5 * ad * ad) / (2 * torch.pi) ** 0.5
+    for got, ref in ((out, want), (db, want), (da, dwant)):
+        err = (got.double().cpu() - ref).abs()
+        assert bool((err <= 2.0 ** -7 * ref.abs() + 1e-7).all()), float((err / (ref.abs() + 1e-7)).max())
+        assert bool(torch.isfinite(got).all())
+
+
 @pytest.mark.parametrize("xdt,ydt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
                                      (torch.bfloat16, torch.bfloat16)])
 @pytest.mark.parametrize("M,H", [(1, 64), (33, 512), (2, 1024), (1000, 2048), (257, 4096), (1, 2048), (600, 384)])
