@@ -234,6 +234,64 @@ rms_norm_fwd_kernel(const TX* __restrict__ x, const TY* __restrict__ delta, TX* 
   }
 }
 
+// The same forward for H = 512 * NCH (NCH = 1, 2, 4, 8): one row per 128-thread group, kept in
+// registers between the sum of squares and the scaling, so the row is read once (see the backward
+// below for the group barrier).
+template <typename TX, typename TY, int NCH>
+__global__ void __launch_bounds__(256, (NCH >= 8 ? 2 : 3))
+rms_norm_fwd_rows_kernel(const TX* __restrict__ x, const TY* __restrict__ delta, TX* __restrict__ x_out,
+                         const float* __restrict__ w, TY* __restrict__ y, float* __restrict__ rstd, int64_t M,
+                         float eps) {
+  constexpr int VEC = 4, TPR = 128, H = NCH * TPR * VEC;
+  __shared__ float part[2][2][4];
+  const int grp = threadIdx.x >> 7, t = threadIdx.x & (TPR - 1), lane = threadIdx.x & 31, wig = t >> 5;
+  float wv[NCH][VEC];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) VecIO<float, VEC>::load(w + (c * TPR + t) * VEC, wv[c]);
+  int par = 0;
+  for (int64_t m = (int64_t)blockIdx.x * 2 + grp; m < M; m += (int64_t)gridDim.x * 2) {
+    const int64_t row = m * H;
+    float v[NCH][VEC];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) VecIO<TX, VEC>::load(x + row + (c * TPR + t) * VEC, v[c]);
+    if (delta != nullptr) {
+      float d[NCH][VEC];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) VecIO<TY, VEC>::load(delta + row + (c * TPR + t) * VEC, d[c]);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) v[c][q] += d[c][q];
+        VecIO<TX, VEC>::store(x_out + row + (c * TPR + t) * VEC, v[c]);
+        if (sizeof(TX) == 2) {  // statistics of the value as stored (a bf16 residual stream)
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) v[c][q] = __bfloat162float(__float2bfloat16(v[c][q]));
+        }
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) ss = fmaf(v[c][q], v[c][q], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) part[grp][par][wig] = ss;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(TPR) : "memory");
+    ss = ((part[grp][par][0] + part[grp][par][1]) + part[grp][par][2]) + part[grp][par][3];
+    par ^= 1;
+    const float inv = rsqrtf(ss / (float)H + eps);
+    if (t == 0) rstd[m] = inv;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      float o[VEC];
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) o[q] = (v[c][q] * inv) * wv[c][q];
+      VecIO<TY, VEC>::store(y + row + (c * TPR + t) * VEC, o);
+    }
+  }
+}
+
 // dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd;  dw partial = sum_rows dy * xhat
 // Each warp walks rows m = warp, warp + nwarps, ...; per-lane column accumulators for dw live in
 // registers (NCH chunks of 4 columns), are summed across the CTA's warps in shared memory in fixed
@@ -484,6 +542,26 @@ static int norm_fwd_impl(const void* x, const void* delta, void* x_out, const fl
   HAWK_REQUIRE(M >= 1 && H >= 4 && H % 4 == 0, HAWK_ERR_SHAPE);
   HAWK_REQUIRE(aligned(x, 16) && aligned(w, 16) && aligned(y, 16) && aligned(delta, 16) && aligned(x_out, 16),
                HAWK_ERR_ALIGN);
+  if (H == 512 || H == 1024 || H == 2048 || H == 4096) {  // rows-in-registers path
+    const unsigned rgrid = (unsigned)(M / 2 + 1 < 148 * 3 ? M / 2 + 1 : 148 * 3);
+#define HAWK_NORM_FROWS_N(TX, TY, N)                                                                               \
+  rms_norm_fwd_rows_kernel<TX, TY, N><<<rgrid, 256, 0, st>>>(static_cast<const TX*>(x), static_cast<const TY*>(delta), \
+                                                             static_cast<TX*>(x_out), w, static_cast<TY*>(y), rstd, M, eps)
+#define HAWK_NORM_FROWS(TX, TY)                        \
+  do {                                                 \
+    if (H == 512) HAWK_NORM_FROWS_N(TX, TY, 1);        \
+    else if (H == 1024) HAWK_NORM_FROWS_N(TX, TY, 2);  \
+    else if (H == 2048) HAWK_NORM_FROWS_N(TX, TY, 4);  \
+    else HAWK_NORM_FROWS_N(TX, TY, 8);                 \
+  } while (0)
+    if (x_dtype == HAWK_F32 && y_dtype == HAWK_BF16) HAWK_NORM_FROWS(float, bf);
+    else if (x_dtype == HAWK_F32) HAWK_NORM_FROWS(float, float);
+    else if (y_dtype == HAWK_BF16) HAWK_NORM_FROWS(bf, bf);
+    else HAWK_NORM_FROWS(bf, float);
+#undef HAWK_NORM_FROWS
+#undef HAWK_NORM_FROWS_N
+    return launch_status();
+  }
   const unsigned grid = grid_for(M, 8);
 #define HAWK_NORM_FWD(TX, TY)                                                                                   \
   rms_norm_fwd_kernel<TX, TY><<<grid, 256, 0, st>>>(static_cast<const TX*>(x), static_cast<const TY*>(delta),    \

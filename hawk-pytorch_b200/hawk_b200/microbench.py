@@ -3,12 +3,15 @@
     python -m hawk_b200.microbench scan      [--B 8 --T 4096 --D 2048 --dtype bf16]
     python -m hawk_b200.microbench conv1d    [--B 8 --T 4096 --D 2048 --dtype bf16]
     python -m hawk_b200.microbench linear_ce [--N 32760 --H 2048 --V 32000]
+    python -m hawk_b200.microbench glue      [--N 32768 --H 2048 --J 6144]   # gelu(a)*b and add+RMSNorm, both ways
     python -m hawk_b200.microbench decode    [--B 256 --D 2048 --layers 24]
     python -m hawk_b200.microbench decode_model [--B 256]   # one cached token of the 1.35 B model, eager vs CUDA graph
 
 Prints one JSON line per kernel with the achieved rate against its algorithmic work:
 scan 8 (forward) / 16 (backward) bytes per element in bf16, conv1d 4 / 6, linear_ce 6*N*H*V flop,
-decode 8*B*D*elem bytes per step.  Inputs are seeded normal draws; Lambda sits on the reference's
+decode 8*B*D*elem bytes per step; glue: the tensors each kernel must read and write once (gelu(a)*b:
+3 / 5 bf16 tensors of N x J; add+RMSNorm with an fp32 residual stream and bf16 branch: 12 / 16 bytes per
+element).  Inputs are seeded normal draws; Lambda sits on the reference's
 0.9..0.999 ring.  Working sets beyond the 126 MB L2 need no flush between launches; smaller ones
 are bracketed by a flush write (`--flush`).
 """
@@ -52,7 +55,8 @@ def _emit(name, ms, work, unit, **extra):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "decode", "decode_model"])
+    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "glue", "decode", "decode_model"])
+    ap.add_argument("--J", type=int, default=6144)
     ap.add_argument("--B", type=int, default=None)
     ap.add_argument("--T", type=int, default=4096)
     ap.add_argument("--D", type=int, default=2048)
@@ -95,6 +99,25 @@ def main(argv=None):
         tb = _time(lambda: ops.conv1d_bwd(go, xv, w), a.iters, a.warmup, flush)
         _emit("conv1d_fwd", tf, 2 * es * n, "GB/s", **shape)
         _emit("conv1d_bwd", tb, 3 * es * n, "GB/s", **shape)
+    elif a.op == "glue":
+        N = a.N if a.N != 8 * 4095 else 8 * 4096
+        gu = torch.randn(N, 2 * a.J, generator=g, device=dev).to(dt)  # the projection whose halves are a and b
+        av, bv = gu[:, :a.J], gu[:, a.J:]
+        go = torch.randn(N, a.J, generator=g, device=dev).to(dt)
+        tf = _time(lambda: ops.gelu_mul_fwd(av, bv), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.gelu_mul_bwd(go, av, bv), a.iters, a.warmup, flush)
+        _emit("gelu_mul_fwd", tf, 3 * es * N * a.J, "GB/s", N=N, J=a.J, dtype=a.dtype)
+        _emit("gelu_mul_bwd", tb, 5 * es * N * a.J, "GB/s", N=N, J=a.J, dtype=a.dtype)
+        del gu, av, bv, go
+        res = torch.randn(N, a.H, generator=g, device=dev)            # fp32 residual stream
+        delta, dy = (torch.randn(N, a.H, generator=g, device=dev).to(dt) for _ in range(2))
+        gres = torch.randn(N, a.H, generator=g, device=dev)
+        w = torch.ones(a.H, device=dev)
+        new_res, y, rstd = ops.add_rms_norm_fwd(res, delta, w, 1e-6, dt)
+        tf = _time(lambda: ops.add_rms_norm_fwd(res, delta, w, 1e-6, dt), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.add_rms_norm_bwd(gres, dy, new_res, w, rstd), a.iters, a.warmup, flush)
+        _emit("add_rms_norm_fwd", tf, (8 + 2 * es) * N * a.H, "GB/s", N=N, H=a.H, dtype=a.dtype)
+        _emit("add_rms_norm_bwd", tb, (12 + 2 * es) * N * a.H, "GB/s", N=N, H=a.H, dtype=a.dtype)
     elif a.op == "linear_ce":
         w = torch.randn(a.V, a.H, generator=g, device=dev) / math.sqrt(a.H)
         act = torch.randn(a.N, a.H, generator=g, device=dev)
