@@ -182,18 +182,20 @@ class Hawk(nn.Module):
 
     def forward(self, x, layer_past: Optional[RNNCache] = None):
         cached = layer_past is not None and self.use_cache and layer_past.current_cache_size > 0
-        xb, y = self.input_xy(x).chunk(2, dim=-1)
+        xb_y = self.input_xy(x)
+        xb, y = xb_y.chunk(2, dim=-1)
         if cached:
             assert x.shape[1] == 1, "cached decode takes one token per call"
             return self._decode(xb, y, layer_past), layer_past
 
-        self.conv1d.out_dtype = xb.dtype  # store the conv result in the activation dtype
-        xc = self.conv1d(xb)
-        # the gate biases go to the scan kernel, which adds them for free and sums their gradients:
-        # the projections write bias-free outputs (no broadcast bias pass, no separate reductions)
-        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, None, self.rg_lru_a_gate.w, None)
+        # conv -> gates -> scan -> gelu(y) * h as one autograd node; the gate biases go to the scan kernel,
+        # which adds them for free and sums their gradients
+        conv = self.conv1d
         gate_bias = torch.stack((self.rg_lru_input_gate.b.reshape(-1), self.rg_lru_a_gate.b.reshape(-1))).float()
-        h = ops.fused_linear_scan(xc, gx, ga, self.rg_lru_a_param.float(), gate_bias=gate_bias)
+        out, h = ops.recurrent_core(xb_y, self._fp32("w", conv.w) if not conv.w.requires_grad else conv.w.float(),
+                                    self._fp32("b", conv.b) if not conv.b.requires_grad else conv.b.float(),
+                                    self.rg_lru_input_gate.w, self.rg_lru_a_gate.w, gate_bias,
+                                    self.rg_lru_a_param.float())
         cache = None
         if self.use_cache:
             assert layer_past is not None, "use_cache=True needs an RNNCache per layer"
@@ -204,7 +206,7 @@ class Hawk(nn.Module):
             layer_past.conv_state.copy_(tail)
             layer_past.update_cache(h[:, -1:])
             cache = layer_past
-        return self.resid_proj(ops.gelu_mul(y, h)), cache
+        return self.resid_proj(out), cache
 
 
 class RNNLayer(nn.Module):

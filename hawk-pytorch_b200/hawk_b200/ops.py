@@ -280,6 +280,34 @@ def _conv_backward(ctx, go):
 conv1d_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
 
 
+@torch.library.custom_op("hawk_b200::conv1d_bwd_into", mutates_args=("dx_out",))
+def conv1d_bwd_into(go: torch.Tensor, x: torch.Tensor, w: torch.Tensor,
+                    dx_out: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """conv1d_bwd with the input gradient written into `dx_out`, a [B,T,D] view that may be row-strided
+    (e.g. one half of the gradient of the projection x was chunked from).  Returns (dw, db)."""
+    lib = _lib.load()
+    B, T, D = x.shape
+    W = w.shape[0]
+    xv = _conv_view(x)
+    assert dx_out.shape == x.shape and dx_out.dtype == x.dtype and _conv_view(dx_out) is dx_out
+    go, w = go.contiguous(), w.contiguous()
+    dw = torch.empty(W, D, dtype=torch.float32, device=x.device)
+    db = torch.empty(D, dtype=torch.float32, device=x.device)
+    ws_bytes = lib.hawk_conv1d_bwd_workspace_bytes(B, T, D, W)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    with _on(x, "conv1d_bwd", 2):
+        _lib.check(lib.hawk_conv1d_bwd(go.data_ptr(), xv.data_ptr(), xv.stride(0), xv.stride(1), w.data_ptr(),
+                                       dx_out.data_ptr(), dx_out.stride(0), dx_out.stride(1), dw.data_ptr(),
+                                       db.data_ptr(), ws.data_ptr(), ws_bytes, B, T, D, W, _dt(go), _dt(xv),
+                                       _stream(x)), "hawk_conv1d_bwd")
+    return dw, db
+
+
+@conv1d_bwd_into.register_fake
+def _(go, x, w, dx_out):
+    return w.new_empty(w.shape, dtype=torch.float32), w.new_empty(w.shape[1], dtype=torch.float32)
+
+
 def temporal_conv1d(x, w, b, *, out_dtype=None):
     """y[b,t,d] = bias[d] + sum_k w[W-1-k,d] x[b,t-k,d] (zero history).  x may be a strided view.
 
@@ -499,6 +527,29 @@ def _(dout, a, b):
     return a.new_empty(a.shape), a.new_empty(a.shape)
 
 
+@torch.library.custom_op("hawk_b200::gelu_mul_bwd_into", mutates_args=("da_out",))
+def gelu_mul_bwd_into(dout: torch.Tensor, a: torch.Tensor, b: torch.Tensor, da_out: torch.Tensor) -> torch.Tensor:
+    """gelu_mul_bwd with d a written into `da_out` (same shape as a; may be a row-strided view such as
+    one half of a wider gradient buffer).  Returns d b."""
+    lib = _lib.load()
+    J = a.shape[-1]
+    av, M, lda = _as_rows(a)
+    bv, _, ldb = _as_rows(b)
+    dv, _, ldd = _as_rows(dout)
+    ov, _, ldo = _as_rows(da_out)
+    assert ov is da_out and da_out.shape == a.shape and da_out.dtype == a.dtype, "da_out must be usable in place"
+    db = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    with _on(a, "gelu_mul_bwd", 1):
+        _lib.check(lib.hawk_gelu_mul_bwd(dv.data_ptr(), ldd, av.data_ptr(), lda, bv.data_ptr(), ldb, ov.data_ptr(), ldo,
+                                         db.data_ptr(), J, M, J, _dt(a), _stream(a)), "hawk_gelu_mul_bwd")
+    return db
+
+
+@gelu_mul_bwd_into.register_fake
+def _(dout, a, b, da_out):
+    return a.new_empty(a.shape)
+
+
 def _gm_setup(ctx, inputs, output):
     ctx.save_for_backward(*inputs)
 
@@ -697,6 +748,69 @@ def block_diag_gates(x, wx, bx, wa, ba):
     the biases to `fused_linear_scan(..., gate_bias=)`."""
     assert (bx is None) == (ba is None)
     return _BlockDiagGates.apply(x, wx, bx, wa, ba)
+
+
+# ---------------------------------------------------------------------------------------------
+# the recurrent branch between its two projections as one autograd node
+# ---------------------------------------------------------------------------------------------
+class _RecurrentCore(torch.autograd.Function):
+    """out = gelu(y) * scan(conv(x_b), gates(conv(x_b))) for xy = [x_b | y] (hawk/hawk.py:164-166,
+    181-199), and h.  The kernels are the ones the separate operators launch; what one node adds is the
+    backward's bookkeeping: d y and d x_b are written straight into the two halves of d xy (no
+    concatenation pass for the chunk), and the gate projections accumulate their input gradient onto
+    the scan's (no separate add pass)."""
+
+    @staticmethod
+    def forward(ctx, xy, conv_w, conv_b, wx, wa, gate_bias, lam):
+        R = xy.shape[-1] // 2
+        nb, bw, _ = wx.shape
+        with torch.autocast("cuda", enabled=False):
+            if _conv_view(xy) is not xy:
+                xy = xy.contiguous()
+            xb, y = xy[..., :R], xy[..., R:]
+            dt = xy.dtype
+            xc = conv1d_fwd(xb, conv_w, conv_b, dt)
+            M = xc.numel() // R
+            gates = torch.empty(2, M, R, dtype=dt, device=xy.device)
+            wxc, wac = wx.to(dt), wa.to(dt)
+            xcb = xc.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
+            torch.bmm(xcb, wxc, out=gates[0].view(M, nb, bw).transpose(0, 1))
+            torch.bmm(xcb, wac, out=gates[1].view(M, nb, bw).transpose(0, 1))
+            gx, ga = gates[0].view(xc.shape), gates[1].view(xc.shape)
+            h = scan_fwd(xc, gx, ga, lam, None, gate_bias)
+            out = gelu_mul_fwd(y, h)
+        ctx.save_for_backward(xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h)
+        ctx.meta = (nb, bw, conv_w.dtype, conv_b.dtype, wx.dtype)
+        ctx.mark_non_differentiable(h)
+        return out, h
+
+    @staticmethod
+    def backward(ctx, dout, _dh):
+        xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h = ctx.saved_tensors
+        nb, bw, cwdt, cbdt, wdt = ctx.meta
+        R = xy.shape[-1] // 2
+        M = xc.numel() // R
+        with torch.autocast("cuda", enabled=False):
+            xb, y = xy[..., :R], xy[..., R:]
+            dxy = torch.empty_like(xy)
+            dh = gelu_mul_bwd_into(dout.to(xy.dtype), y, h, dxy[..., R:])
+            dxc, dgx, dga, dlam, _, dgb = scan_bwd(xc, gx, ga, lam, None, gate_bias, h, dh)
+            gxb = dgx.view(M, nb, bw).transpose(0, 1)
+            gab = dga.view(M, nb, bw).transpose(0, 1)
+            xcT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
+            dwx = torch.bmm(xcT, gxb)
+            dwa = torch.bmm(xcT, gab)
+            dxcb = dxc.view(M, nb, bw).transpose(0, 1)
+            torch.baddbmm(dxcb, gxb, wxc.transpose(1, 2), out=dxcb)  # d xc (scan) += d gx Wx^T + d ga Wa^T
+            torch.baddbmm(dxcb, gab, wac.transpose(1, 2), out=dxcb)
+            dcw, dcb = conv1d_bwd_into(dxc, xb, conv_w, dxy[..., :R])
+        return dxy, dcw.to(cwdt), dcb.to(cbdt), dwx.to(wdt), dwa.to(wdt), dgb, dlam
+
+
+def recurrent_core(xy, conv_w, conv_b, wx, wa, gate_bias, lam):
+    """(gelu(y) * h, h) from the input projection xy = [x_b | y] of the recurrent block; conv taps/bias,
+    Lambda and gate_bias [2, R] in fp32, gate weights [nb, bw, bw]."""
+    return _RecurrentCore.apply(xy, conv_w, conv_b, wx, wa, gate_bias, lam)
 
 
 # ---------------------------------------------------------------------------------------------

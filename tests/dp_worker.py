@@ -22,9 +22,21 @@ def _scan_with_bias(x, gx, ga, lam, h0=None, gate_bias=None):
     return omodel.scan(x, gx, ga, lam)
 
 
+def _recurrent_core(xy, conv_w, conv_b, wx, wa, gate_bias, lam):
+    """hawk/hawk.py:164-166,181-199 from oracle statements: (gelu(y) * h, h)."""
+    xb, y = xy.chunk(2, dim=-1)
+    xc = omodel.conv1d(xb, conv_w, conv_b)
+    nb, bw, _ = wx.shape
+    gx = omodel.block_diag_linear(xc, wx, gate_bias[0].view(nb, bw))
+    ga = omodel.block_diag_linear(xc, wa, gate_bias[1].view(nb, bw))
+    h = omodel.scan(xc, gx, ga, lam)
+    return F.gelu(y) * h, h
+
+
 # oracle statements standing in for the kernels (the product has no CPU path; only tests do this)
 SUBSTITUTES = {
     "fused_linear_scan": _scan_with_bias,
+    "recurrent_core": _recurrent_core,
     "fused_cross_entropy": lambda w, a, l: F.cross_entropy(F.linear(a, w), l),
     "rms_norm": lambda x, w, eps=1e-6, out_dtype=None: omodel.rms_norm(x, w),
     "add_rms_norm": lambda r, d, w, eps=1e-6, out_dtype=None: (

@@ -161,3 +161,39 @@ def test_add_rms_norm_matches_torch(xdt, ydt, M, H):
     _, y3 = ops.add_rms_norm(rd3, dd3, wd.detach(), 1e-6, out_dtype=ydt)
     y3.backward(g_y.cuda())
     assert torch.isfinite(rd3.grad).all() and rel_l2(dd3.grad.float().cpu(), rd3.grad.float().cpu()) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,T,R,nb", [(2, 33, 64, 2), (3, 200, 256, 4), (1, 1, 128, 16)])
+def test_recurrent_core_equals_the_separate_operators(dtype, B, T, R, nb):
+    """One autograd node for conv -> gates -> scan -> gelu(y) * h: same outputs and the same gradients as
+    the chain of separate operators (chunk, Conv1D, block-diagonal gates with biases, scan, gelu_mul)."""
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(B * 100 + T + R)
+    bw = R // nb
+    xy = torch.randn(B, T, 2 * R, generator=g).to(dtype)
+    cw, cb = 0.3 * torch.randn(4, R, generator=g), 0.1 * torch.randn(R, generator=g)
+    wx, wa = (torch.randn(nb, bw, bw, generator=g) / bw ** 0.5 for _ in range(2))
+    bx, ba = (0.2 * torch.randn(nb, bw, generator=g) for _ in range(2))
+    lam = torch.rand(R, generator=g) * 4 - 6
+    go = torch.randn(B, T, R, generator=g).to(dtype)
+
+    def leaves():
+        return [t.clone().cuda().requires_grad_(True) for t in (xy, cw, cb, wx, wa, bx, ba, lam)]
+
+    a = leaves()
+    out, h = ops.recurrent_core(a[0], a[1], a[2], a[3], a[4], torch.stack((a[5].reshape(-1), a[6].reshape(-1))), a[7])
+    assert not h.requires_grad
+    out.backward(go.cuda())
+    b = leaves()
+    xb, y = b[0].chunk(2, dim=-1)
+    xc = ops.temporal_conv1d(xb, b[1], b[2], out_dtype=dtype)
+    gx, ga = ops.block_diag_gates(xc, b[3], b[5], b[4], b[6])
+    h2 = ops.fused_linear_scan(xc, gx, ga, b[7])
+    out2 = ops.gelu_mul(y, h2)
+    out2.backward(go.cuda())
+    tol = 2e-3 if dtype == torch.float32 else 3e-2  # fp32 bmm may run as TF32; bf16 rounds gate + bias once more
+    assert rel_l2(out.float().cpu(), out2.float().cpu()) <= tol and rel_l2(h.float().cpu(), h2.float().cpu()) <= tol
+    for name, p, q in zip(("xy", "conv_w", "conv_b", "wx", "wa", "bx", "ba", "lam"), a, b):
+        assert p.grad is not None and p.grad.shape == q.grad.shape, name
+        assert rel_l2(p.grad.float().cpu(), q.grad.float().cpu()) <= tol, (name, rel_l2(p.grad.float().cpu(), q.grad.float().cpu()))
