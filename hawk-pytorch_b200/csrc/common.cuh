@@ -201,6 +201,12 @@ __device__ __forceinline__ float sqrt_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float tanh_approx(float x) {  // relative error 2^-11, saturates to +-1
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <bool FAST>
 __device__ __forceinline__ float sigmoid_f(float g) {
   if (FAST) {

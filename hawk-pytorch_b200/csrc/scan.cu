@@ -35,32 +35,20 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+#ifndef HAWK_SCAN_BWD_EXP_GATES
+#define HAWK_SCAN_BWD_EXP_GATES 1  // backward gates from 2^x + shared reciprocal (1) or tanh (0)
+#endif
+
 template <typename T>
 struct SmemPair;  // two adjacent channels read back from the staging ring
-// ld_gate reads a gate pre-activation pair g.  The bf16 path floors it, while still packed (one
-// max.bf16x2 for both channels), at the lane's constant from gate_floor(): -42 - bias, so that
-// g + bias >= -42.4 whatever the bias is.  sigmoid(-42) is 6e-19 already, and the floor keeps
-// 2^(-(g + bias) log2 e) below 2^62 and the shared reciprocal of the two gates' product finite
-// without per-channel clamps.  The fp32 path uses expf and needs no floor.
 template <>
 struct SmemPair<float> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
-  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p, uint32_t) { return ld(p); }
-  static __device__ __forceinline__ uint32_t gate_floor(float, float) { return 0u; }
 };
 template <>
 struct SmemPair<__nv_bfloat16> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) {
     return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
-  }
-  static __device__ __forceinline__ float2 ld_gate(const unsigned char* p, uint32_t floor2) {
-    uint32_t v = *reinterpret_cast<const uint32_t*>(p), r;
-    asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(floor2));
-    return unpack_bf16x2(r);
-  }
-  // b0, b1: the lane's two bias values (0 without a bias); rounding to bf16 moves the floor by < 0.4
-  static __device__ __forceinline__ uint32_t gate_floor(float b0, float b1) {
-    return pack_bf16x2(-42.f - b0, -42.f - b1);
   }
 };
 
@@ -71,63 +59,96 @@ __device__ __forceinline__ float gate_scale(float lam) {
   return FAST ? kGateC * sp * kLog2e : kGateC * sp;
 }
 
-// The lane's gate-bias pair [bias of channel ch, of ch+1] from row `row` of the optional [2, D] table:
-// `term` in the form gates2 consumes, `floor2` for SmemPair::ld_gate.  FAST folds the bias into the
-// multiply that feeds 2^x, so the add costs no instruction: -log2(e) (g + b) = fma(g, -log2 e,
-// -log2(e) b).  The sum is not rounded to the storage type (the reference rounds gate + bias to bf16
-// before its scan, hawk/scan_fused.py:428).
-template <typename T, bool FAST>
-__device__ __forceinline__ void gate_bias_term(const float* __restrict__ gbias, int row, int D, int ch,
-                                               float2& term, uint32_t& floor2) {
+// The lane's gate-bias pair [bias of channel ch, of ch+1] from row `row` of the optional [2, D] table,
+// in the form gates2 consumes.  FAST evaluates sigmoid(g + b) = 0.5 + 0.5 tanh(0.5 g + 0.5 b), so the
+// bias rides on the multiply that halves g: the add costs no instruction.  The sum is not rounded to
+// the storage type (the reference rounds gate + bias to bf16 before its scan, hawk/scan_fused.py:428).
+template <bool FAST>
+__device__ __forceinline__ float2 gate_bias_term(const float* __restrict__ gbias, int row, int D, int ch) {
   float b0 = 0.f, b1 = 0.f;
   if (gbias != nullptr) {
     b0 = gbias[(size_t)row * D + ch];
     b1 = gbias[(size_t)row * D + ch + 1];
   }
-  term = FAST ? make_float2(-kLog2e * b0, -kLog2e * b1) : make_float2(b0, b1);
-  floor2 = SmemPair<T>::gate_floor(b0, b1);
+  return FAST ? make_float2(0.5f * b0, 0.5f * b1) : make_float2(b0, b1);
 }
 
 // ---- arithmetic on a lane's channel pair -------------------------------------------------------
-// sm_100 has packed fp32x2 add/mul/fma: one issue slot for both channels.  The kernels are issue
-// bound (about 40 instructions per element), so the FAST path does its FP32 work two at a time.
+// sm_100 has packed fp32x2 add/mul/fma: one issue slot for both channels.  The kernels are bound by
+// instruction issue and by the MUFU pipe (profile: XU pipe 63 % busy, MIO-queue stalls on top), so the
+// FAST path does its FP32 work two at a time and spends one MUFU operation per sigmoid:
+// tanh.approx (relative error 2^-11, an eighth of a bf16 rounding step; saturates to +-1 for any
+// input, so nothing needs clamping) instead of 2^x and a reciprocal.
 
-// i = sigmoid(gx) and r = sigmoid(ga).  FAST shares one reciprocal between the two:
-// 1/(1+eg) = (1+ea) / ((1+eg)(1+ea)), three MUFU operations instead of four.  The exponent is
-// capped so that the product stays finite (sigmoid(-30) is 9e-14 already).
+// i = sigmoid(gx) and r = sigmoid(ga), scalar form
 template <bool FAST>
 __device__ __forceinline__ void sigmoid_pair(float gx, float ga, float& i, float& r) {
   if (FAST) {
-    const float u = 1.f + ex2_approx(fminf(-kLog2e * gx, 43.f));
-    const float v = 1.f + ex2_approx(fminf(-kLog2e * ga, 43.f));
-    const float w = rcp_approx(u * v);
-    i = v * w;
-    r = u * w;
+    i = fmaf(tanh_approx(0.5f * gx), 0.5f, 0.5f);
+    r = fmaf(tanh_approx(0.5f * ga), 0.5f, 0.5f);
   } else {
     i = 1.f / (1.f + expf(-gx));
     r = 1.f / (1.f + expf(-ga));
   }
 }
 
-// both gates of both channels; bx, ba: gate_bias_term of the two gates
+// tanh((g + b) / 2) of both gates of both channels; bx, ba: gate_bias_term of the two gates
+__device__ __forceinline__ void gate_tanh2(float2 gx, float2 ga, float2 bx, float2 ba, float2& tx, float2& ta) {
+  tx = fma2(gx, f2(0.5f), bx);
+  ta = fma2(ga, f2(0.5f), ba);
+  tx.x = tanh_approx(tx.x);
+  tx.y = tanh_approx(tx.y);
+  ta.x = tanh_approx(ta.x);
+  ta.y = tanh_approx(ta.y);
+}
+
+// both gates of both channels
 template <bool FAST>
 __device__ __forceinline__ void gates2(float2 gx, float2 ga, float2 bx, float2 ba, float2& i, float2& r) {
   if (FAST) {
-    float2 tx = fma2(gx, f2(-kLog2e), bx), ta = fma2(ga, f2(-kLog2e), ba);
-    tx.x = ex2_approx(tx.x);  // at most 2^62: the inputs were floored when loaded (SmemPair::ld_gate)
-    tx.y = ex2_approx(tx.y);
-    ta.x = ex2_approx(ta.x);
-    ta.y = ex2_approx(ta.y);
-    const float2 u = add2(tx, f2(1.f)), v = add2(ta, f2(1.f));
-    float2 w = mul2(u, v);
-    w.x = rcp_approx(w.x);
-    w.y = rcp_approx(w.y);
-    i = mul2(v, w);
-    r = mul2(u, w);
+    float2 tx, ta;
+    gate_tanh2(gx, ga, bx, ba, tx, ta);
+    i = fma2(tx, f2(0.5f), f2(0.5f));
+    r = fma2(ta, f2(0.5f), f2(0.5f));
   } else {
     sigmoid_pair<false>(gx.x + bx.x, ga.x + ba.x, i.x, r.x);
     sigmoid_pair<false>(gx.y + bx.y, ga.y + ba.y, i.y, r.y);
   }
+}
+
+// The same two sigmoids from 2^x and ONE shared reciprocal per channel: 1/(1+eg) = (1+ea) / ((1+eg)(1+ea)),
+// three MUFU operations for two sigmoids.  Measured in the backward kernel, this form is ~4 % faster
+// than the tanh form (which wins in the forward), so the backward keeps it.  The gate inputs come
+// packed (bf16x2) and are floored, still packed, at the lane's constant -42 - bias (`floor2`, from
+// exp_gate_terms), so that g + bias >= -42.4 whatever the bias: each 2^x stays below 2^62 and the
+// product finite without per-channel clamps; sigmoid(-42) is 6e-19 already.
+__device__ __forceinline__ float2 ld_floored_bf16x2(const unsigned char* p, uint32_t floor2) {
+  uint32_t v = *reinterpret_cast<const uint32_t*>(p), r;
+  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(floor2));
+  return unpack_bf16x2(r);
+}
+__device__ __forceinline__ void exp_gate_terms(const float* __restrict__ gbias, int row, int D, int ch,
+                                               float2& term, uint32_t& floor2) {
+  float b0 = 0.f, b1 = 0.f;
+  if (gbias != nullptr) {
+    b0 = gbias[(size_t)row * D + ch];
+    b1 = gbias[(size_t)row * D + ch + 1];
+  }
+  term = make_float2(-kLog2e * b0, -kLog2e * b1);  // -log2(e) (g + b) = fma(g, -log2 e, term)
+  floor2 = pack_bf16x2(-42.f - b0, -42.f - b1);    // rounding to bf16 moves the floor by < 0.4
+}
+__device__ __forceinline__ void gates2_exp(float2 gx, float2 ga, float2 bx, float2 ba, float2& i, float2& r) {
+  float2 tx = fma2(gx, f2(-kLog2e), bx), ta = fma2(ga, f2(-kLog2e), ba);
+  tx.x = ex2_approx(tx.x);
+  tx.y = ex2_approx(tx.y);
+  ta.x = ex2_approx(ta.x);
+  ta.y = ex2_approx(ta.y);
+  const float2 u = add2(tx, f2(1.f)), v = add2(ta, f2(1.f));
+  float2 w = mul2(u, v);
+  w.x = rcp_approx(w.x);
+  w.y = rcp_approx(w.y);
+  i = mul2(v, w);
+  r = mul2(u, w);
 }
 
 // a = exp(k r) for both channels (k already in log2 units on the FAST path).
@@ -153,14 +174,18 @@ __device__ __forceinline__ void fwd_coeffs(float x, float gx, float ga, float k,
   beta = (x * i) * sqrtf(1.f - expf(2.f * la));  // :99-105
 }
 
-// (a, beta) of one row for the lane's channel pair
+// (a, beta) of one row for the lane's channel pair.  FAST never forms r: k r = (k/2) tanh + k/2.
 template <bool FAST>
 __device__ __forceinline__ void fwd_coeffs2(float2 x, float2 gx, float2 ga, float2 bx, float2 ba, float2 k,
                                             float2& a, float2& beta) {
   if (FAST) {
-    float2 i, r;
-    gates2<true>(gx, ga, bx, ba, i, r);
-    a = decay2<true>(k, r);
+    float2 tx, ta;
+    gate_tanh2(gx, ga, bx, ba, tx, ta);
+    const float2 i = fma2(tx, f2(0.5f), f2(0.5f));
+    const float2 kh = mul2(k, f2(0.5f));  // loop invariant
+    float2 la = fma2(ta, kh, kh);
+    a.x = ex2_approx(la.x);
+    a.y = ex2_approx(la.y);
     const float2 v = fma2(neg2(a), a, f2(1.f));
     float2 m;
     m.x = sqrt_approx(v.x);
@@ -243,10 +268,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   const float2 lam2 = *reinterpret_cast<const float2*>(lam + ch);
   const float2 k2 = make_float2(gate_scale<FAST>(lam2.x), gate_scale<FAST>(lam2.y));
   // gate biases [2, D]: row 0 for gx, row 1 for ga (zero when absent)
-  float2 bgx, bga;
-  uint32_t fgx, fga;
-  gate_bias_term<T, FAST>(gbias, 0, D, ch, bgx, fgx);
-  gate_bias_term<T, FAST>(gbias, 1, D, ch, bga, fga);
+  const float2 bgx = gate_bias_term<FAST>(gbias, 0, D, ch), bga = gate_bias_term<FAST>(gbias, 1, D, ch);
   if (threadIdx.x < LPR) {
     state[0][threadIdx.x] =
         h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch0 + 2 * threadIdx.x) : make_float2(0.f, 0.f);
@@ -313,8 +335,8 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     for (int r = 0; r < R; ++r) {
       if (FULL || t0 + r < T_len) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
-        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld_gate(row + G::IN_BYTES, fgx),
-                          SmemPair<T>::ld_gate(row + 2 * G::IN_BYTES, fga), bgx, bga, k2, a[r], be[r]);
+        fwd_coeffs2<FAST>(SmemPair<T>::ld(row), SmemPair<T>::ld(row + G::IN_BYTES),
+                          SmemPair<T>::ld(row + 2 * G::IN_BYTES), bgx, bga, k2, a[r], be[r]);
       } else {  // past the end: identity step
         a[r] = f2(1.f);
         be[r] = f2(0.f);
@@ -383,10 +405,11 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   // factor that turns d(log a) into d(ga)/(r(1-r)):  C * softplus(lam), in natural-log units
   const float2 q2 = FAST ? make_float2(k2.x * (1.f / kLog2e), k2.y * (1.f / kLog2e)) : k2;
   const float2 h0v = h0 ? *reinterpret_cast<const float2*>(h0 + (size_t)b * D + ch) : make_float2(0.f, 0.f);
-  float2 bgx, bga;
+  const float2 bgx = gate_bias_term<FAST>(gbias, 0, D, ch), bga = gate_bias_term<FAST>(gbias, 1, D, ch);
+  float2 egx, ega;  // the same biases for the 2^x form of the gates (bf16 path)
   uint32_t fgx, fga;
-  gate_bias_term<T, FAST>(gbias, 0, D, ch, bgx, fgx);
-  gate_bias_term<T, FAST>(gbias, 1, D, ch, bga, fga);
+  exp_gate_terms(gbias, 0, D, ch, egx, fgx);
+  exp_gate_terms(gbias, 1, D, ch, ega, fga);
   if (threadIdx.x < LPR) state[0][threadIdx.x] = make_float2(0.f, 0.f);  // c_T = 0
 
   static_assert((STAGES & (STAGES - 1)) == 0, "STAGES must be a power of two");
@@ -457,8 +480,10 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       if (FULL || tt - r >= 0) {
         const unsigned char* row = st + r * G::NSUB * G::ROWB;
         gov = SmemPair<T>::ld(row + G::IN_BYTES);
-        gates2<FAST>(SmemPair<T>::ld_gate(row + 3 * G::IN_BYTES, fgx), SmemPair<T>::ld_gate(row, fga), bgx, bga, ig[r],
-                     rg[r]);
+        if (FAST && HAWK_SCAN_BWD_EXP_GATES)
+          gates2_exp(ld_floored_bf16x2(row + 3 * G::IN_BYTES, fgx), ld_floored_bf16x2(row, fga), egx, ega, ig[r], rg[r]);
+        else
+          gates2<FAST>(SmemPair<T>::ld(row + 3 * G::IN_BYTES), SmemPair<T>::ld(row), bgx, bga, ig[r], rg[r]);
         a[r] = decay2<FAST>(k2, rg[r]);
       } else {
         rg[r] = ig[r] = f2(0.f);
