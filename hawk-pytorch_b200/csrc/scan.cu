@@ -520,13 +520,15 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
       c = mul2(av, dh);
       float2 o_dx, o_dgx, o_dga;
       if (FAST) {
-        // below the clamp (1 - a^2 < 2.5e-7, i.e. a within 1.3e-7 of 1) m = v * 2000 stands in
-        // for sqrt(v): both are < 5e-4 there, which bf16 storage cannot resolve against dh
+        // v = 1 - a^2 + 2.4e-7 (two ulps of 1) instead of the reference's clamp max(1 - a^2, 2.5e-7) under
+        // the square root's derivative: one packed add instead of two scalar maxima.  Where the two
+        // differ (a within 1e-4 of 1) m = sqrt(v) is off by < 5e-4 absolute, which bf16 storage cannot
+        // resolve against dh; the reciprocal root stays finite at a = 1 as with the clamp.
         const float2 a2 = mul2(av, av);
-        const float2 v = add2(f2(1.f), neg2(a2));
+        const float2 v = add2(f2(1.0000002384185791f), neg2(a2));
         float2 rs;
-        rs.x = rsqrt_approx(fmaxf(v.x, 2.5e-7f));
-        rs.y = rsqrt_approx(fmaxf(v.y, 2.5e-7f));
+        rs.x = rsqrt_approx(v.x);
+        rs.y = rsqrt_approx(v.y);
         const float2 m = mul2(v, rs);
         const float2 xi = mul2(iv, xv);
         const float2 dm = mul2(dh, m);
