@@ -672,13 +672,14 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
 // Launch shape.  A CTA scans all of T for its channel group, so the grid is B * D / CW CTAs of equal
 // cost.  Measured on B200 (bf16), alone and inside a training step (where the SM clock sits near
 // 1.55 GHz under the board's power limit and the kernels turn compute bound): the forward is best
-// with narrow groups (CW = 16, 128-thread CTAs, ~7 per SM: even load on every SM), the backward with
-// CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
-// with CW = 32 to double the CTA count.
+// with narrow groups (CW = 16: 128-thread CTAs, ~7 per SM, even load on every SM; 256-thread CTAs when
+// there are few groups, e.g. one long sequence: B1 T65536 D4096 4.16 against 4.03 TB/s), the backward
+// with CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
+// with CW = 32 to double the CTA count.  (512-thread CTAs measured slower in both directions.)
 static int pick_cfg(int B, int D, bool backward) {
   if (const char* e = getenv("HAWK_SCAN_CFG")) return atoi(e);  // tuning/debug override
   const bool many = (int64_t)B * (D / 64) >= 200;
-  if (!backward) return many ? 3 : 4;
+  if (!backward) return many ? 3 : 6;
   return many ? 5 : 1;
 }
 
@@ -715,6 +716,7 @@ extern "C" int hawk_scan_fwd(const void* x, const void* gx, const void* ga, cons
       case 3: HAWK_FWD(bf, 8, 4, 8, 2, 7, true);
       case 4: HAWK_FWD(bf, 8, 4, 8, 4, 4, true);
       case 5: HAWK_FWD(bf, 4, 4, 8, 4, 7, true);
+      case 6: HAWK_FWD(bf, 8, 8, 8, 4, 2, true);
       default: return HAWK_ERR_UNSUPPORTED;
     }
   }
