@@ -159,6 +159,20 @@ static void gelu_launch_shape(int64_t M, int nvec, dim3& block, unsigned& grid) 
   grid = (unsigned)(want < cap ? want : cap);
 }
 
+// fp32 -> bf16 of a contiguous array, 8 elements per thread step (two 16-byte loads, one 16-byte store)
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                            int64_t n) {
+  const int64_t nvec = n / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    VecIO<float, 8>::load(src + i * 8, v);
+    VecIO<__nv_bfloat16, 8>::store(dst + i * 8, v);
+  }
+  if (blockIdx.x == 0) {  // ragged tail
+    for (int64_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) dst[i] = __float2bfloat16(src[i]);
+  }
+}
+
 // ---- RMSNorm: one warp per row, two passes over the row (the second hits L1/L2) ----------------
 // With `delta` the row is first updated, x_out = x + delta (the residual add that precedes every norm
 // in the block, hawk/hawk.py:229-234), and the norm is taken of the sum: one pass instead of two ops.
@@ -489,6 +503,15 @@ static unsigned grid_for(int64_t work_items, int per_block) {
 
 using namespace hawk;
 using bf = __nv_bfloat16;
+
+extern "C" int hawk_cast_f32_bf16(const float* src, void* dst, int64_t n, void* stream) {
+  HAWK_REQUIRE(src && dst, HAWK_ERR_NULL);
+  HAWK_REQUIRE(n >= 1, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(aligned(src, 16) && aligned(dst, 16), HAWK_ERR_ALIGN);
+  cast_f32_bf16_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, static_cast<bf*>(dst), n);
+  return launch_status();
+}
 
 extern "C" int hawk_gelu_mul_fwd(const void* a, int64_t lda, const void* b, int64_t ldb, void* out, int64_t ldo,
                                  int64_t M, int J, int dtype, void* stream) {

@@ -124,13 +124,23 @@ class RNNCache:
                 f"filled={self.current_cache_size}, conv_width={self.temporal_conv_width})")
 
 
+class Linear(nn.Linear):
+    """nn.Linear without bias (same parameter name and state-dict key) whose forward goes through
+    `ops.linear`: under CUDA bf16 autocast the weight cast and the weight-gradient cast are fused away."""
+
+    def forward(self, x):
+        if self.bias is not None:
+            return super().forward(x)
+        return ops.linear(x, self.weight)
+
+
 class MLP(nn.Module):
     """Gated GELU feed-forward (hawk/hawk.py:61-86); `resid_proj` starts at zero."""
 
     def __init__(self, config: HawkConfig):
         super().__init__()
-        self.gate_up_proj = nn.Linear(config.hidden_size, 2 * config.intermediate_size, bias=False)
-        self.resid_proj = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+        self.gate_up_proj = Linear(config.hidden_size, 2 * config.intermediate_size, bias=False)
+        self.resid_proj = Linear(config.intermediate_size, config.hidden_size, bias=False)
         _lecun_normal_(self.gate_up_proj.weight, config.hidden_size)
         nn.init.zeros_(self.resid_proj.weight)
 
@@ -146,11 +156,11 @@ class Hawk(nn.Module):
         self.config = config
         self.use_cache = use_cache
         R = config.recurrent_size
-        self.input_xy = nn.Linear(config.hidden_size, 2 * R, bias=False)
+        self.input_xy = Linear(config.hidden_size, 2 * R, bias=False)
         self.rg_lru_input_gate = BlockDiagonalLinear(R, config.num_blocks)
         self.rg_lru_a_gate = BlockDiagonalLinear(R, config.num_blocks)
         self.rg_lru_a_param = nn.Parameter(torch.empty(R, dtype=torch.float32))
-        self.resid_proj = nn.Linear(R, config.hidden_size, bias=False)
+        self.resid_proj = Linear(R, config.hidden_size, bias=False)
         self.conv1d = ops.Conv1D(width=R, temporal_width=config.conv_width)
         self._fp32_cache = {}
         ring_init_(self.rg_lru_a_param)

@@ -184,6 +184,11 @@ int hawk_add_rms_norm_bwd(const void* dy, const void* x_sum, const float* w, con
                           void* dx, void* ddelta, float* dw, void* workspace, size_t workspace_bytes, int64_t M,
                           int H, int x_dtype, int y_dtype, void* stream);
 
+/* fp32 -> bf16 (round to nearest even) of n contiguous elements: the weight cast that CUDA autocast runs
+ * before every bf16 GEMM of an fp32 parameter (torch's type-converting copy, reached from F.linear in
+ * hawk/hawk.py:75-86,110-116 under torch.autocast), as one vectorised pass.  src, dst 16-byte aligned. */
+int hawk_cast_f32_bf16(const float* src, void* dst, int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

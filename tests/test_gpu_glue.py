@@ -197,3 +197,45 @@ def test_recurrent_core_equals_the_separate_operators(dtype, B, T, R, nb):
     for name, p, q in zip(("xy", "conv_w", "conv_b", "wx", "wa", "bx", "ba", "lam"), a, b):
         assert p.grad is not None and p.grad.shape == q.grad.shape, name
         assert rel_l2(p.grad.float().cpu(), q.grad.float().cpu()) <= tol, (name, rel_l2(p.grad.float().cpu(), q.grad.float().cpu()))
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 4099, 1 << 20, (1 << 22) + 3])
+def test_cast_bf16_is_bit_exact_round_to_nearest_even(n):
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=g) * torch.exp(8 * torch.randn(n, generator=g))
+    special = torch.tensor([0.0, -0.0, float("inf"), -float("inf"), 1.00390625, 1.01171875, 3.3e38, -3.4e38, 1e-40,
+                            float("nan")])
+    x[:min(n, special.numel())] = special[:min(n, special.numel())]
+    got = ops.cast_bf16(x.cuda())
+    want = x.cuda().to(torch.bfloat16)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("lead,K,N", [((3, 50), 64, 96), ((1000,), 512, 256), ((2, 7, 9), 128, 40)])
+def test_autocast_linear_matches_f_linear(lead, K, N):
+    """ops.linear under bf16 autocast: the same output and input gradient as F.linear (bit for bit: same
+    rounded operands, same GEMM), the weight gradient in fp32 straight from the GEMM (at least as close to
+    the exact product as autocast's bf16-rounded one); outside autocast it is F.linear."""
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(K + N)
+    x = torch.randn(*lead, K, generator=g)
+    w = torch.randn(N, K, generator=g) / K ** 0.5
+    go = torch.randn(*lead, N, generator=g)
+    outs = []
+    for fn in (ops.linear, F.linear):
+        xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = fn(xd, wd)
+        assert y.dtype == torch.bfloat16
+        y.backward(go.cuda().to(y.dtype))
+        assert xd.grad.dtype == torch.float32 and wd.grad.dtype == torch.float32
+        outs.append((y.detach(), xd.grad, wd.grad))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    xb, gb = x.bfloat16().double().reshape(-1, K), go.bfloat16().double().reshape(-1, N)
+    exact = gb.t() @ xb
+    e_mine, e_auto = rel_l2(outs[0][2].cpu(), exact), rel_l2(outs[1][2].cpu(), exact)
+    assert e_mine <= 1e-5 and e_mine <= e_auto + 1e-7, (e_mine, e_auto)
+    xd, wd = x.cuda().requires_grad_(True), w.cuda().requires_grad_(True)
+    y = ops.linear(xd, wd)  # no autocast: plain fp32 F.linear
+    assert y.dtype == torch.float32 and rel_l2(y.detach().cpu(), F.linear(x, w)) <= 2e-3
