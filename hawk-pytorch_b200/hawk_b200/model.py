@@ -128,10 +128,18 @@ class Linear(nn.Linear):
     """nn.Linear without bias (same parameter name and state-dict key) whose forward goes through
     `ops.linear`: under CUDA bf16 autocast the weight cast and the weight-gradient cast are fused away."""
 
+    # bf16 copy of the weight kept current by an optimiser that updates both in one pass
+    # (train.FusedAdamW); valid only while the fp32 weight still has the version it was written for
+    weight_bf16: Optional[torch.Tensor] = None
+    weight_bf16_version: int = -1
+
     def forward(self, x):
         if self.bias is not None:
             return super().forward(x)
-        return ops.linear(x, self.weight)
+        wb = self.weight_bf16
+        if wb is not None and (self.weight_bf16_version != self.weight._version or wb.device != self.weight.device):
+            wb = None
+        return ops.linear(x, self.weight, wb)
 
 
 class MLP(nn.Module):

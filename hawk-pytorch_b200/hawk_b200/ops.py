@@ -779,10 +779,11 @@ class _AutocastLinear(torch.autograd.Function):
     being written in bf16 and cast afterwards (so it is also a little more precise than the reference's)."""
 
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, wb):
         with torch.autocast("cuda", enabled=False):
             xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-            wb = cast_bf16(w.detach())
+            if wb is None:  # no up-to-date bf16 copy from the optimiser: cast now
+                wb = cast_bf16(w.detach())
             y = F.linear(xb, wb)
         ctx.save_for_backward(xb, wb)
         ctx.x_dtype = x.dtype
@@ -802,16 +803,29 @@ class _AutocastLinear(torch.autograd.Function):
                     dx = dx.to(ctx.x_dtype)
             if ctx.needs_input_grad[1]:
                 dw = torch.mm(dy2.t(), xb.reshape(-1, xb.shape[-1]), out_dtype=torch.float32)
-        return dx, dw
+        return dx, dw, None
 
 
-def linear(x, w):
-    """F.linear(x, w) without bias.  Under CUDA autocast with an fp32 weight it runs as `_AutocastLinear`;
+def linear(x, w, w_bf16=None):
+    """F.linear(x, w) without bias.  Under CUDA autocast with an fp32 weight it runs as `_AutocastLinear`
+    (`w_bf16`: an up-to-date bf16 copy of w, e.g. the one `FusedAdamW` writes; cast here when None);
     anywhere else it is F.linear itself."""
     if (x.is_cuda and w.dtype == torch.float32 and torch.is_autocast_enabled("cuda")
             and torch.get_autocast_dtype("cuda") == torch.bfloat16):
-        return _AutocastLinear.apply(x, w)
+        return _AutocastLinear.apply(x, w, w_bf16)
     return F.linear(x, w)
+
+
+def adamw_step_(p, g, m, v, p_bf16, lr, beta1, beta2, eps, weight_decay, step):
+    """In-place AdamW update of one fp32 tensor through the C ABI (see hawk_adamw_step); called by
+    `train.FusedAdamW` under no_grad, outside any graph capture or compilation."""
+    lib = _lib.load()
+    assert p.is_cuda and p.dtype == g.dtype == m.dtype == v.dtype == torch.float32
+    assert p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous()
+    assert p_bf16 is None or (p_bf16.dtype == torch.bfloat16 and p_bf16.is_contiguous() and p_bf16.shape == p.shape)
+    with _on(p, "adamw_step", 1):
+        _lib.check(lib.hawk_adamw_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _ptr(p_bf16), p.numel(),
+                                       lr, beta1, beta2, eps, weight_decay, step, _stream(p)), "hawk_adamw_step")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -846,10 +860,13 @@ class _RecurrentCore(torch.autograd.Function):
         ctx.save_for_backward(xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h)
         ctx.meta = (nb, bw, conv_w.dtype, conv_b.dtype, wx.dtype)
         ctx.mark_non_differentiable(h)
+        ctx.set_materialize_grads(False)  # no zero-filled [B,T,R] gradient for h on every backward
         return out, h
 
     @staticmethod
     def backward(ctx, dout, _dh):
+        if dout is None:
+            return (None,) * 7
         xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h = ctx.saved_tensors
         nb, bw, cwdt, cbdt, wdt = ctx.meta
         R = xy.shape[-1] // 2

@@ -31,6 +31,49 @@ def init_distributed(backend: Optional[str] = None) -> tuple:
     return rank, local_rank, world
 
 
+class FusedAdamW(torch.optim.Optimizer):
+    """torch.optim.AdamW's update (decoupled weight decay, bias correction) with one kernel per fp32
+    parameter tensor that also writes the bf16 copy of the updated weight for the model's `Linear`
+    layers (`shadow_modules`: modules with `.weight`, `.weight_bf16`, `.weight_bf16_version`), so the next
+    forward casts nothing.  State keys follow torch.optim.AdamW (`step`, `exp_avg`, `exp_avg_sq`)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, shadow_modules=()):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self._shadow = {id(m.weight): m for m in shadow_modules}
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        from . import ops
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                st["step"] += 1
+                g = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                mod = self._shadow.get(id(p))
+                wb = None
+                if mod is not None:
+                    wb = mod.weight_bf16
+                    if wb is None or wb.shape != p.shape or wb.device != p.device:
+                        wb = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+                ops.adamw_step_(p, g, st["exp_avg"], st["exp_avg_sq"], wb, group["lr"], b1, b2, group["eps"],
+                                group["weight_decay"], st["step"])
+                torch.autograd.graph.increment_version(p)  # the kernel wrote p behind autograd's back
+                if mod is not None:
+                    mod.weight_bf16, mod.weight_bf16_version = wb, p._version
+        return loss
+
+
 class Trainer:
     """Model + AdamW (+ DDP when world_size > 1).  `step(ids)` runs forward (bf16 autocast, fused
     cross-entropy with labels = inputs), backward, gradient all-reduce and the optimiser update."""
@@ -46,8 +89,14 @@ class Trainer:
             from torch.nn.parallel import DistributedDataParallel as DDP
             ids = [self.device.index] if self.device.type == "cuda" else None
             self.ddp = DDP(self.model, device_ids=ids, gradient_as_bucket_view=True, bucket_cap_mb=bucket_cap_mb)
-        fused = self.device.type == "cuda"
-        self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.1, fused=fused)
+        # HAWK_B200_OPTIMIZER=torch selects torch.optim.AdamW(fused=True) instead (for A/B timing)
+        if self.device.type == "cuda" and os.environ.get("HAWK_B200_OPTIMIZER", "fused") != "torch":
+            from .model import Linear
+            shadows = [m for m in self.model.modules() if isinstance(m, Linear) and m.bias is None] if self.autocast else []
+            self.opt = FusedAdamW(self.model.parameters(), lr=lr, weight_decay=0.1, shadow_modules=shadows)
+        else:
+            self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.1,
+                                         fused=self.device.type == "cuda")
 
     def step(self, ids: torch.Tensor) -> torch.Tensor:
         net = self.ddp if self.ddp is not None else self.model

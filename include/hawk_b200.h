@@ -189,6 +189,14 @@ int hawk_add_rms_norm_bwd(const void* dy, const void* x_sum, const float* w, con
  * hawk/hawk.py:75-86,110-116 under torch.autocast), as one vectorised pass.  src, dst 16-byte aligned. */
 int hawk_cast_f32_bf16(const float* src, void* dst, int64_t n, void* stream);
 
+/* One AdamW step (decoupled weight decay, torch.optim.AdamW's update rule with bias correction for
+ * step number `step` >= 1) on n contiguous fp32 elements, in place in p, m (first moment) and v (second
+ * moment); g is the gradient.  p_bf16 (may be NULL) receives the bf16 rounding of the updated p, so the
+ * next forward needs no cast pass.  No counterpart in the reference, which stops at loss.backward()
+ * (README.md:36) and leaves the optimiser to the user; this is the update torch.optim.AdamW would make. */
+int hawk_adamw_step(float* p, const float* g, float* m, float* v, void* p_bf16, int64_t n, float lr, float beta1,
+                    float beta2, float eps, float weight_decay, int64_t step, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
