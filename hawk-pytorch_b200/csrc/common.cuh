@@ -35,6 +35,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// scalar conversions for kernels templated on the storage type
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
 // packed fp32x2 arithmetic of sm_100: one issue slot for both channels of a pair
 __device__ __forceinline__ float2 f2(float v) { return make_float2(v, v); }
 __device__ __forceinline__ float2 neg2(float2 v) { return make_float2(-v.x, -v.y); }

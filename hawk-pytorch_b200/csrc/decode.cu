@@ -74,6 +74,154 @@ decode_rglru_step_kernel(const T* __restrict__ x, const T* __restrict__ gx, cons
   if (h_out) VecIO<T, VEC>::store(h_out + o, hv);
 }
 
+
+// ---- the whole recurrent branch of one cached token in ONE launch --------------------------------
+// out = gelu(y) * h for xy = [x_b | y]: conv step (with the cache roll), both block-diagonal gate
+// projections, the RG-LRU step (state updated in place) and the output gate.  A CTA owns one gate
+// block (bw channels: a gate's output needs exactly the block's bw conv outputs) and TB = 16 batch
+// rows; the block's two weight matrices, conv outputs and gate pre-activations sit in shared memory.  Per token and layer this
+// replaces five launches (conv step, two gate GEMMs, RG-LRU step, gelu * h); the arithmetic is tiny
+// (2 * B * R * bw MACs per gate), so the step is launch bound and fewer launches is the whole gain.
+constexpr int kDecTB = 16;
+constexpr int kDecIT = 8;  // elements per thread: TB * 128 / 256
+
+template <typename T, typename TS, typename TW>
+__global__ void __launch_bounds__(256)
+decode_block_step_kernel(const T* __restrict__ xy, int64_t ld_xy, TS* __restrict__ conv_state,
+                         const float* __restrict__ cw, const float* __restrict__ cb, const TW* __restrict__ wx,
+                         const TW* __restrict__ wa, const float* __restrict__ bx, const float* __restrict__ ba,
+                         const float* __restrict__ lam, TS* __restrict__ state, T* __restrict__ out, int B, int R,
+                         int bw, int W) {
+  extern __shared__ __align__(16) unsigned char dsm_raw[];
+  float* xcT = reinterpret_cast<float*>(dsm_raw);  // [bw][TB]   conv outputs, transposed
+  float* g = xcT + (size_t)bw * kDecTB;            // [2][TB][bw] gate pre-activations
+  TW* ws = reinterpret_cast<TW*>(g + (size_t)2 * kDecTB * bw);  // [2][bw][bw] the block's two weight matrices
+  const int blk = blockIdx.x, b0 = blockIdx.y * kDecTB, ch0 = blk * bw;
+
+  // Every global input of the launch is requested before anything waits: a thread owns up to kDecIT
+  // (batch row, channel) elements (TB * bw <= 256 * kDecIT since bw <= 128) and loads their conv window,
+  // new input, y, state and per-channel constants into registers in one unrolled pass, so the kernel pays
+  // one memory round trip instead of one per element (the first version: 28 us per launch, stalled on loads).
+  const int nelem = kDecTB * bw;
+  float xn[kDecIT], yv[kDecIT], sv[kDecIT], lv[kDecIT], cacc[kDecIT], win[kDecIT][3];
+  int eb[kDecIT], ec[kDecIT];
+  bool ok[kDecIT];
+#pragma unroll
+  for (int it = 0; it < kDecIT; ++it) {
+    const int idx = threadIdx.x + it * 256;
+    const int b = idx / bw, c = idx - b * bw, bg = b0 + b, ch = ch0 + c;
+    eb[it] = b;
+    ec[it] = c;
+    ok[it] = idx < nelem && bg < B;
+    xn[it] = yv[it] = sv[it] = lv[it] = cacc[it] = 0.f;
+    win[it][0] = win[it][1] = win[it][2] = 0.f;
+    if (ok[it]) {
+      const T* xr = xy + (int64_t)bg * ld_xy;
+      xn[it] = to_float(xr[ch]);
+      yv[it] = to_float(xr[R + ch]);
+      sv[it] = to_float(state[(int64_t)bg * R + ch]);
+      lv[it] = lam[ch];
+      const TS* sp = conv_state + ((int64_t)bg * (W - 1)) * R + ch;
+      float acc = fmaf(cw[(int64_t)(W - 1) * R + ch], xn[it], cb[ch]);
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {  // state row j is x[t-(W-1)+j], paired with w[j]
+        if (j < W - 1) {
+          win[it][j] = to_float(sp[(int64_t)j * R]);
+          acc = fmaf(cw[(int64_t)j * R + ch], win[it][j], acc);
+        }
+      }
+      cacc[it] = acc;
+    }
+  }
+
+  // stage both weight matrices of the block in shared memory (16-byte copies, all in flight at once)
+  {
+    const int nel = bw * bw;
+    const TW* src0 = wx + (int64_t)blk * nel;
+    const TW* src1 = wa + (int64_t)blk * nel;
+    const bool vec = (nel * (int)sizeof(TW)) % 16 == 0 && (reinterpret_cast<uintptr_t>(src0) % 16) == 0 &&
+                     (reinterpret_cast<uintptr_t>(src1) % 16) == 0;
+    if (vec) {
+      const int n16 = nel * (int)sizeof(TW) / 16;
+      const uint4* s0 = reinterpret_cast<const uint4*>(src0);
+      const uint4* s1 = reinterpret_cast<const uint4*>(src1);
+      uint4* d0 = reinterpret_cast<uint4*>(ws);
+      uint4* d1 = reinterpret_cast<uint4*>(ws + nel);
+#pragma unroll 4
+      for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+        d0[i] = __ldg(s0 + i);
+        d1[i] = __ldg(s1 + i);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nel; i += blockDim.x) {
+        ws[i] = src0[i];
+        ws[nel + i] = src1[i];
+      }
+    }
+  }
+
+  // conv outputs to shared memory, and the cache roll (hawk/hawk.py:168-179, hawk/cache.py:37-43)
+#pragma unroll
+  for (int it = 0; it < kDecIT; ++it) {
+    const int idx = threadIdx.x + it * 256;
+    if (idx < nelem) xcT[ec[it] * kDecTB + eb[it]] = cacc[it];
+    if (ok[it]) {
+      TS* sp = conv_state + ((int64_t)(b0 + eb[it]) * (W - 1)) * R + ch0 + ec[it];
+#pragma unroll
+      for (int j = 1; j < 3; ++j)
+        if (j < W - 1) sp[(int64_t)(j - 1) * R] = from_float<TS>(win[it][j]);
+      if (W > 1) sp[(int64_t)(W - 2) * R] = from_float<TS>(xn[it]);
+    }
+  }
+  __syncthreads();
+
+  // both gate projections of the block: g[gate][b][j] = bias[j] + sum_k xc[b][k] w[k][j]  (external.py:224-233)
+  for (int o = threadIdx.x; o < 2 * bw; o += blockDim.x) {
+    const int gate = o / bw, j = o - gate * bw;
+    const TW* wp = ws + (size_t)gate * bw * bw + j;
+    const float bias = (gate ? ba : bx)[ch0 + j];
+    float acc[kDecTB];
+#pragma unroll
+    for (int b = 0; b < kDecTB; ++b) acc[b] = bias;
+#pragma unroll 4
+    for (int k = 0; k < bw; ++k) {
+      const float wv = to_float(wp[k * bw]);
+      const float4* xr = reinterpret_cast<const float4*>(xcT + k * kDecTB);
+#pragma unroll
+      for (int q = 0; q < kDecTB / 4; ++q) {
+        const float4 xv = xr[q];
+        acc[4 * q] = fmaf(xv.x, wv, acc[4 * q]);
+        acc[4 * q + 1] = fmaf(xv.y, wv, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(xv.z, wv, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(xv.w, wv, acc[4 * q + 3]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kDecTB; ++b) g[((size_t)gate * kDecTB + b) * bw + j] = acc[b];
+  }
+  __syncthreads();
+
+  // RG-LRU step (hawk/hawk.py:137-151,193-198) and the output gate gelu(y) * h (:134-135)
+#pragma unroll
+  for (int it = 0; it < kDecIT; ++it) {
+    if (!ok[it]) continue;
+    const int b = eb[it], c = ec[it];
+    const float l = lv[it];
+    const float sp = l > 20.f ? l : softplus_f(l);
+    const float i = sigmoid_f<false>(g[(size_t)b * bw + c]);
+    const float r = sigmoid_f<false>(g[((size_t)kDecTB + b) * bw + c]);
+    const float la = kGateC * r * sp;
+    const float a = expf(la);
+    const float m = sqrtf(1.f - expf(2.f * la));
+    const int64_t so = (int64_t)(b0 + b) * R + ch0 + c;
+    const float h = fmaf(a, sv[it], (cacc[it] * i) * m);
+    state[so] = from_float<TS>(h);
+    const float y = yv[it];
+    const float gl = 0.5f * y * (1.f + erff(y * 0.70710678118654752f));
+    out[so] = from_float<T>(gl * h);
+  }
+}
+
 template <typename T, typename TS>
 static int conv_step_dispatch(const void* x_new, int64_t xrs, void* conv_state, const float* w, const float* bias,
                               void* y, int B, int D, int W, cudaStream_t st) {
@@ -142,4 +290,53 @@ extern "C" int hawk_decode_rglru_step(const void* x, const void* gx, const void*
   if (dtype == HAWK_BF16) return rglru_step_dispatch<bf, float>(x, gx, ga, lam, state, h_out, B, D, st);
   if (state_dtype == HAWK_BF16) return rglru_step_dispatch<float, bf>(x, gx, ga, lam, state, h_out, B, D, st);
   return rglru_step_dispatch<float, float>(x, gx, ga, lam, state, h_out, B, D, st);
+}
+
+
+namespace hawk {
+template <typename T, typename TS, typename TW>
+static int block_step_launch(const void* xy, int64_t ld_xy, void* conv_state, const float* cw, const float* cb,
+                             const void* wx, const void* wa, const float* bx, const float* ba, const float* lam,
+                             void* state, void* out, int B, int R, int bw, int W, cudaStream_t st) {
+  const size_t smem = (size_t)3 * kDecTB * bw * sizeof(float) + (size_t)2 * bw * bw * sizeof(TW);
+  dim3 grid((unsigned)(R / bw), (unsigned)((B + kDecTB - 1) / kDecTB));
+  auto kern = decode_block_step_kernel<T, TS, TW>;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return HAWK_ERR_LAUNCH;
+  }
+  kern<<<grid, 256, smem, st>>>(
+      static_cast<const T*>(xy), ld_xy, static_cast<TS*>(conv_state), cw, cb, static_cast<const TW*>(wx),
+      static_cast<const TW*>(wa), bx, ba, lam, static_cast<TS*>(state), static_cast<T*>(out), B, R, bw, W);
+  return launch_status();
+}
+}  // namespace hawk
+
+extern "C" int hawk_decode_block_step(const void* xy, int64_t xy_row_stride, void* conv_state, const float* conv_w,
+                                      const float* conv_b, const void* wx, const void* wa, const float* bx,
+                                      const float* ba, const float* lam, void* state, void* out, int B, int R,
+                                      int block_width, int W, int dtype, int state_dtype, int weight_dtype,
+                                      void* stream) {
+  HAWK_REQUIRE(xy && conv_w && conv_b && wx && wa && bx && ba && lam && state && out && (conv_state || W == 1),
+               HAWK_ERR_NULL);
+  HAWK_REQUIRE(valid_dtype(dtype) && valid_dtype(state_dtype) && valid_dtype(weight_dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(B >= 1 && R >= 1 && block_width >= 1 && R % block_width == 0 && xy_row_stride >= 2 * (int64_t)R,
+               HAWK_ERR_SHAPE);
+  HAWK_REQUIRE(W >= 1 && W <= 4 && block_width <= 128, HAWK_ERR_UNSUPPORTED);  // weights staged in shared memory
+  HAWK_REQUIRE((int64_t)((B + kDecTB - 1) / kDecTB) <= 65535, HAWK_ERR_SHAPE);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define HAWK_DEC_BLOCK(T, TS, TW)                                                                                  \
+  return block_step_launch<T, TS, TW>(xy, xy_row_stride, conv_state, conv_w, conv_b, wx, wa, bx, ba, lam, state, out, \
+                                      B, R, block_width, W, st)
+  const bool xb = dtype == HAWK_BF16, sb = state_dtype == HAWK_BF16, wb = weight_dtype == HAWK_BF16;
+  if (xb && sb && wb) HAWK_DEC_BLOCK(bf, bf, bf);
+  if (xb && sb) HAWK_DEC_BLOCK(bf, bf, float);
+  if (xb && wb) HAWK_DEC_BLOCK(bf, float, bf);
+  if (xb) HAWK_DEC_BLOCK(bf, float, float);
+  if (sb && wb) HAWK_DEC_BLOCK(float, bf, bf);
+  if (sb) HAWK_DEC_BLOCK(float, bf, float);
+  if (wb) HAWK_DEC_BLOCK(float, float, bf);
+  HAWK_DEC_BLOCK(float, float, float);
+#undef HAWK_DEC_BLOCK
 }

@@ -31,6 +31,7 @@ SIGNATURES = {
                                 c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_conv_step": (c_int, [_P, c_int64, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_decode_rglru_step": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "hawk_decode_block_step": (c_int, [_P, c_int64] + [_P] * 10 + [c_int] * 7 + [_P]),
     "hawk_adamw_step": (c_int, [_P, _P, _P, _P, _P, c_int64, c_float, c_float, c_float, c_float, c_float, c_int64, _P]),
     "hawk_cast_f32_bf16": (c_int, [_P, _P, c_int64, _P]),
     "hawk_gelu_mul_fwd": (c_int, [_P, c_int64, _P, c_int64, _P, c_int64, c_int64, c_int, c_int, _P]),

@@ -186,15 +186,22 @@ class Hawk(nn.Module):
             self._fp32_cache[name] = hit
         return hit[1]
 
-    def _decode(self, xb, y, cache: RNNCache):
-        """One cached token: xb, y [B,1,R] (hawk/hawk.py:168-179,193-199)."""
-        x_new = xb[:, 0]
+    def _decode(self, xb_y, cache: RNNCache):
+        """One cached token: xb_y [B,1,2R] (hawk/hawk.py:168-179,193-199)."""
         conv = self.conv1d
-        xc = ops.decode_conv_step(x_new, cache.conv_state, self._fp32("w", conv.w), self._fp32("b", conv.b))
-        gx, ga = ops.block_diag_gates(xc, self.rg_lru_input_gate.w, self.rg_lru_input_gate.b,
-                                      self.rg_lru_a_gate.w, self.rg_lru_a_gate.b)
+        gi, ga_ = self.rg_lru_input_gate, self.rg_lru_a_gate
         state = cache.recc_state[:, 0]
-        h = ops.decode_rglru_step(xc, gx, ga, self._fp32("lam", self.rg_lru_a_param), state)
+        cw, cb, lam = self._fp32("w", conv.w), self._fp32("b", conv.b), self._fp32("lam", self.rg_lru_a_param)
+        if gi.block_width <= 128 and conv.temporal_width <= 4:
+            # conv step, both gate projections, RG-LRU step and gelu(y) * h in one launch
+            out = ops.decode_block_step(xb_y[:, 0], cache.conv_state, cw, cb, gi.w, ga_.w, self._fp32("bx", gi.b),
+                                        self._fp32("ba", ga_.b), lam, state)
+            cache.current_cache_size = 1
+            return self.resid_proj(out[:, None])
+        xb, y = xb_y.chunk(2, dim=-1)
+        xc = ops.decode_conv_step(xb[:, 0], cache.conv_state, cw, cb)
+        gx, ga = ops.block_diag_gates(xc, gi.w, gi.b, ga_.w, ga_.b)
+        h = ops.decode_rglru_step(xc, gx, ga, lam, state)
         cache.current_cache_size = 1
         return self.resid_proj(ops.gelu_mul(y, h[:, None]))
 
@@ -204,7 +211,7 @@ class Hawk(nn.Module):
         xb, y = xb_y.chunk(2, dim=-1)
         if cached:
             assert x.shape[1] == 1, "cached decode takes one token per call"
-            return self._decode(xb, y, layer_past), layer_past
+            return self._decode(xb_y, layer_past), layer_past
 
         # conv -> gates -> scan -> gelu(y) * h as one autograd node; the gate biases go to the scan kernel,
         # which adds them for free and sums their gradients

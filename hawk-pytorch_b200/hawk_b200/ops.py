@@ -366,6 +366,37 @@ def _(x_new, conv_state, w, b):
     return x_new.new_empty(x_new.shape)
 
 
+@torch.library.custom_op("hawk_b200::decode_block_step", mutates_args=("conv_state", "state"))
+def decode_block_step(xy: torch.Tensor, conv_state: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor,
+                      wx: torch.Tensor, wa: torch.Tensor, bx: torch.Tensor, ba: torch.Tensor, lam: torch.Tensor,
+                      state: torch.Tensor) -> torch.Tensor:
+    """One cached token through the whole recurrent branch in one launch: xy [B,2R] = [x_b | y] (row-strided
+    ok), conv_state [B,W-1,R] and state [B,R] updated in place, gate weights [nb,bw,bw] (fp32 or bf16),
+    biases / conv taps / Lambda fp32.  Returns gelu(y) * h, [B,R] in xy's dtype."""
+    lib = _lib.load()
+    B, R2 = xy.shape
+    R = R2 // 2
+    nb, bw, _ = wx.shape
+    if xy.stride(1) != 1:
+        xy = xy.contiguous()
+    assert conv_state.is_contiguous() and state.is_contiguous() and state.shape == (B, R)
+    assert conv_state.dtype == state.dtype and wx.dtype == wa.dtype and nb * bw == R
+    wx, wa, bx, ba = wx.contiguous(), wa.contiguous(), bx.contiguous(), ba.contiguous()
+    out = torch.empty(B, R, dtype=xy.dtype, device=xy.device)
+    with _on(xy, "decode_block_step", 1):
+        _lib.check(lib.hawk_decode_block_step(xy.data_ptr(), xy.stride(0), conv_state.data_ptr(), conv_w.data_ptr(),
+                                              conv_b.data_ptr(), wx.data_ptr(), wa.data_ptr(), bx.data_ptr(),
+                                              ba.data_ptr(), lam.data_ptr(), state.data_ptr(), out.data_ptr(), B, R,
+                                              bw, conv_w.shape[0], _dt(xy), _dt(state), _dt(wx), _stream(xy)),
+                   "hawk_decode_block_step")
+    return out
+
+
+@decode_block_step.register_fake
+def _(xy, conv_state, conv_w, conv_b, wx, wa, bx, ba, lam, state):
+    return xy.new_empty(xy.shape[0], xy.shape[1] // 2)
+
+
 @torch.library.custom_op("hawk_b200::decode_rglru_step", mutates_args=("state",))
 def decode_rglru_step(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
                       state: torch.Tensor) -> torch.Tensor:

@@ -128,6 +128,16 @@ int hawk_decode_conv_step(const void* x_new, int64_t x_row_stride, void* conv_st
 int hawk_decode_rglru_step(const void* x, const void* gx, const void* ga, const float* lam,
                            void* state, void* h_out, int B, int D, int dtype, int state_dtype,
                            void* stream);
+/* The same cached token for the whole recurrent branch in one launch: conv step (+ cache roll), both
+ * block-diagonal gate projections with their biases (hawk/external.py:224-233 at hawk/hawk.py:181-182),
+ * RG-LRU step (state in place) and out = gelu(y) * h (hawk/hawk.py:134-135,199).  xy [B, >= 2R] rows of
+ * [x_b | y] (`dtype`, row stride in elements); conv_state [B,W-1,R] and state [B,R] (`state_dtype`);
+ * wx, wa [R/block_width, block_width, block_width] (`weight_dtype`), bx, ba, lam, conv_w [W,R], conv_b
+ * fp32; out [B,R] `dtype`.  block_width <= 128, W <= 4. */
+int hawk_decode_block_step(const void* xy, int64_t xy_row_stride, void* conv_state, const float* conv_w,
+                           const float* conv_b, const void* wx, const void* wa, const float* bx, const float* ba,
+                           const float* lam, void* state, void* out, int B, int R, int block_width, int W,
+                           int dtype, int state_dtype, int weight_dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Fused linear + cross-entropy.  Replaces CrossEntropyLoopedFused.forward

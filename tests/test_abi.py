@@ -103,3 +103,16 @@ def test_glue_ce_and_decode_argument_validation_needs_no_gpu():
     assert lib.hawk_decode_rglru_step(p, p, p, p, None, p, 2, 64, 1, 1, None) == -1
     # the no-allocation backward refuses what its built-in scratch cannot hold
     assert lib.hawk_scan_bwd_noalloc(p, p, p, p, None, p, p, p, p, p, p, None, 129, 8, 2048, 1, None) == -9
+
+
+def test_cast_and_adamw_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)
+    assert lib.hawk_cast_f32_bf16(None, p, 8, None) == -1
+    assert lib.hawk_cast_f32_bf16(p, p, 0, None) == -2
+    assert lib.hawk_cast_f32_bf16(ctypes.c_void_p(4100), p, 8, None) == -4
+    adam = (1e-3, 0.9, 0.999, 1e-8, 0.1)
+    assert lib.hawk_adamw_step(p, None, p, p, None, 8, *adam, 1, None) == -1      # gradient missing
+    assert lib.hawk_adamw_step(p, p, p, p, None, 0, *adam, 1, None) == -2         # n < 1
+    assert lib.hawk_adamw_step(p, p, p, p, None, 8, *adam, 0, None) == -2         # step counts from 1
+    assert lib.hawk_adamw_step(ctypes.c_void_p(4098), p, p, p, None, 8, *adam, 1, None) == -4

@@ -130,3 +130,38 @@ def test_decode_steps_reproduce_the_full_scan():
         assert max_rel(y, xc[:, t]) <= FP32_TOL
         ht = decode_rglru_step(y, gx[:, t].contiguous(), ga[:, t].contiguous(), lam, st)
         assert max_rel(ht, h[:, t]) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,R,nb", [(1, 64, 8), (3, 128, 16), (37, 512, 16), (256, 2048, 16), (20, 512, 4), (5, 6, 3)])
+@pytest.mark.parametrize("dtype,sdtype,wdtype", [(torch.float32, torch.float32, torch.float32),
+                                                 (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                                 (torch.bfloat16, torch.float32, torch.float32)])
+def test_fused_decode_block_step_matches_oracle(B, R, nb, dtype, sdtype, wdtype):
+    """conv step + both gate projections + RG-LRU step + gelu(y) * h in one launch == the oracle's
+    statements of the four pieces chained (with the caches it leaves behind)."""
+    import torch.nn.functional as F
+    from hawk_b200 import ops
+    from oracle import model as omodel
+    g = torch.Generator().manual_seed(B + R + nb)
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    bw = R // nb
+    xy = rnd(B, 2 * R).to(dtype)
+    conv_state, state = rnd(B, 3, R).to(sdtype), rnd(B, R).to(sdtype)
+    cw, cb = 0.3 * rnd(4, R), 0.1 * rnd(R)
+    wx, wa = ((rnd(nb, bw, bw) / bw ** 0.5).to(wdtype) for _ in range(2))
+    bx, ba = 0.2 * rnd(nb, bw), 0.2 * rnd(nb, bw)
+    lam = oscan.rnn_param_ring(R, generator=g)
+    cs, st = conv_state.cuda().clone(), state.cuda().clone()
+    out = ops.decode_block_step(xy.cuda(), cs, cw.cuda(), cb.cuda(), wx.cuda(), wa.cuda(), bx.cuda(), ba.cuda(),
+                                lam.cuda(), st)
+    d = torch.float64
+    xc, wcs = odec.conv_step(xy[:, :R].float(), conv_state.float(), cw, cb, compute=d)
+    gx = omodel.block_diag_linear(xc.to(d), wx.to(d), bx.to(d))
+    ga = omodel.block_diag_linear(xc.to(d), wa.to(d), ba.to(d))
+    wh = odec.rglru_step(xc.to(d), gx, ga, lam, state.float(), compute=d)
+    want = F.gelu(xy[:, R:].to(d)) * wh
+    tol = FP32_TOL if dtype == sdtype == torch.float32 else BF16_TOL
+    assert out.dtype == dtype and out.shape == (B, R)
+    assert rel_l2(out.float().cpu(), want) <= tol
+    assert rel_l2(st.float().cpu(), wh) <= (FP32_TOL if sdtype == torch.float32 else BF16_TOL)
+    assert torch.equal(cs.float().cpu(), wcs.float().to(sdtype).float())  # the roll is exact
