@@ -43,35 +43,81 @@ class FusedAdamW(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
-        from . import ops
+        from . import _lib, ops
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        lib = _lib.load()
+        touched = []
         for group in self.param_groups:
             b1, b2 = group["betas"]
+            lr, eps, wd = group["lr"], group["eps"], group["weight_decay"]
             for p in group["params"]:
-                if p.grad is None:
+                g = p.grad
+                if g is None:
                     continue
                 st = self.state[p]
                 if not st:
-                    st["step"] = 0
-                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
-                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                    self._init_state(p, st)
                 st["step"] += 1
-                g = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                if not g.is_contiguous():
+                    g = g.contiguous()
+                # pointers of p, m, v and the bf16 copy are fixed for the life of the state: one ctypes
+                # call per tensor with cached addresses keeps the host side of 300+ launches to ~2 ms
+                p_ptr, m_ptr, v_ptr, wb_ptr, n, dev = st["_args"]
+                if p_ptr != p.data_ptr():  # the parameter was moved or re-allocated since the state was made
+                    self._bind(p, st)
+                    p_ptr, m_ptr, v_ptr, wb_ptr, n, dev = st["_args"]
+                if dev != torch.cuda.current_device():
+                    with torch.cuda.device(dev):
+                        rc = lib.hawk_adamw_step(p_ptr, g.data_ptr(), m_ptr, v_ptr, wb_ptr, n, lr, b1, b2, eps, wd,
+                                                 st["step"], torch.cuda.current_stream().cuda_stream)
+                else:
+                    rc = lib.hawk_adamw_step(p_ptr, g.data_ptr(), m_ptr, v_ptr, wb_ptr, n, lr, b1, b2, eps, wd,
+                                             st["step"], torch.cuda.current_stream().cuda_stream)
+                _lib.check(rc, "hawk_adamw_step")
+                touched.append(p)
+        if touched:
+            torch.autograd.graph.increment_version(touched)  # the kernels wrote p behind autograd's back
+            for p in touched:
                 mod = self._shadow.get(id(p))
-                wb = None
                 if mod is not None:
-                    wb = mod.weight_bf16
-                    if wb is None or wb.shape != p.shape or wb.device != p.device:
-                        wb = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
-                ops.adamw_step_(p, g, st["exp_avg"], st["exp_avg_sq"], wb, group["lr"], b1, b2, group["eps"],
-                                group["weight_decay"], st["step"])
-                torch.autograd.graph.increment_version(p)  # the kernel wrote p behind autograd's back
-                if mod is not None:
-                    mod.weight_bf16, mod.weight_bf16_version = wb, p._version
+                    mod.weight_bf16, mod.weight_bf16_version = self.state[p]["_shadow"], p._version
+            if ops.LOG.enabled:
+                ops.LOG.counts["adamw_step"] = ops.LOG.counts.get("adamw_step", 0) + len(touched)
         return loss
+
+    def _init_state(self, p, st):
+        assert p.is_cuda and p.dtype == torch.float32 and p.is_contiguous(), "FusedAdamW: contiguous fp32 CUDA parameters"
+        st["step"] = 0
+        st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+        st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+        self._bind(p, st)
+
+    def _bind(self, p, st):
+        """(Re)build what is derived from the state: the bf16 copy's buffer and the cached addresses."""
+        for k in ("exp_avg", "exp_avg_sq"):
+            if st[k].device != p.device or not st[k].is_contiguous():
+                st[k] = st[k].to(p.device).contiguous()
+        wb = None
+        if id(p) in self._shadow:
+            wb = torch.empty(p.shape, dtype=torch.bfloat16, device=p.device)
+        st["_shadow"] = wb
+        st["_args"] = (p.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(),
+                       None if wb is None else wb.data_ptr(), p.numel(), p.device.index)
+
+    def state_dict(self):
+        sd = super().state_dict()  # cached addresses and the bf16 copies are derived, not state
+        sd["state"] = {k: {kk: vv for kk, vv in v.items() if not kk.startswith("_")} for k, v in sd["state"].items()}
+        return sd
+
+    def load_state_dict(self, state_dict):
+        super().load_state_dict(state_dict)
+        for p, st in self.state.items():
+            if st:
+                st["step"] = int(st["step"])
+                self._bind(p, st)
 
 
 class Trainer:

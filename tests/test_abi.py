@@ -116,3 +116,16 @@ def test_cast_and_adamw_argument_validation_needs_no_gpu():
     assert lib.hawk_adamw_step(p, p, p, p, None, 0, *adam, 1, None) == -2         # n < 1
     assert lib.hawk_adamw_step(p, p, p, p, None, 8, *adam, 0, None) == -2         # step counts from 1
     assert lib.hawk_adamw_step(ctypes.c_void_p(4098), p, p, p, None, 8, *adam, 1, None) == -4
+
+
+def test_decode_block_step_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)
+    ptrs = [p] * 10  # conv_state .. out
+    ok_tail = (1, 1, 1, None)  # dtype, state_dtype, weight_dtype, stream
+    assert lib.hawk_decode_block_step(None, 4096, *ptrs, 2, 2048, 128, 4, *ok_tail) == -1
+    assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 100, 4, *ok_tail) == -2   # R % block_width
+    assert lib.hawk_decode_block_step(p, 2048, *ptrs, 2, 2048, 128, 4, *ok_tail) == -2   # row stride < 2R
+    assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 256, 4, *ok_tail) == -7   # block wider than 128
+    assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 128, 5, *ok_tail) == -7   # conv width
+    assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 128, 4, 1, 1, 9, None) == -3

@@ -36,6 +36,18 @@ def test_fused_adamw_matches_torch_adamw(misaligned):
         assert all(a._version > v for a, v in zip(mine, v0))  # autograd sees the in-place update
         for a, b in zip(mine, ref):
             assert float((a - b).abs().max()) <= 2e-6 * float(b.abs().max()), step
+    # state round trip: a fresh optimiser loaded from the state dict continues identically
+    o3 = FusedAdamW(mine, **kw)
+    o3.load_state_dict(o1.state_dict())
+    assert all(not k.startswith("_") for st in o1.state_dict()["state"].values() for k in st)
+    for a, b in zip(mine, ref):
+        gr = torch.randn(a.shape, generator=g, device="cuda")
+        a.grad, b.grad = gr.clone(), gr.clone()
+    o3.step()
+    o2.step()
+    for a, b in zip(mine, ref):
+        assert float((a - b).abs().max()) <= 2e-6 * float(b.abs().max())
+    o1 = o3
     for a, b in zip(mine, ref):
         sa, sb = o1.state[a], o2.state[b]
         assert float((sa["exp_avg"] - sb["exp_avg"]).abs().max()) <= 1e-6 * float(sb["exp_avg"].abs().max())
