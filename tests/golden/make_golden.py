@@ -35,7 +35,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-ref_path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path to a checkout of fattorib/hawk-pytorch>")
+ref_path = sys.argv[1]
 sys.path.insert(0, ref_path)
 
 import hawk  # noqa: E402  (the reference package)

@@ -213,7 +213,7 @@ def test_graphed_decode_equals_eager_decode(bf16_weights):
 
 
 def test_config1_block_shape_matches_oracle():
-    """BASELINE config 1: one recurrent block, forward and backward, bf16 autocast, B=8, T=2048,
+    """Benchmark configuration 1: one recurrent block, forward and backward, bf16 autocast, B=8, T=2048,
     hidden = recurrent = 512, 16 gate blocks, conv width 4, reference init (seed 0) with the zero
     resid_proj re-drawn so that the output is not identically zero."""
     import hawk_b200.model as M
@@ -243,7 +243,7 @@ def test_config1_block_shape_matches_oracle():
 
 
 def test_config2_readme_model_step():
-    """BASELINE config 2 at full size (vocab 32000, hidden 512, 8 layers, B=16, T=2048, labels = inputs,
+    """Benchmark configuration 2 at full size (vocab 32000, hidden 512, 8 layers, B=16, T=2048, labels = inputs,
     bf16 autocast, fused linear-CE).  At the reference init the loss is ln(32000) and only lm_head has
     a gradient; the following AdamW steps move the loss below it."""
     import hawk_b200.model as M
