@@ -137,8 +137,9 @@ class Linear(nn.Linear):
         if self.bias is not None:
             return super().forward(x)
         wb = self.weight_bf16
-        if wb is not None and (self.weight_bf16_version != self.weight._version or wb.device != self.weight.device):
-            wb = None
+        if wb is not None and (torch.compiler.is_compiling() or self.weight_bf16_version != self.weight._version
+                               or wb.device != self.weight.device):
+            wb = None  # stale, or traced code (which must not depend on a tensor's version): cast instead
         return ops.linear(x, self.weight, wb)
 
 
