@@ -675,8 +675,12 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
 // with narrow groups (CW = 16: 128-thread CTAs, ~7 per SM, even load on every SM; 256-thread CTAs when
 // there are few groups, e.g. one long sequence: B1 T65536 D4096 4.16 against 4.03 TB/s), the backward
 // with CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
-// with CW = 32 to double the CTA count.  (512-thread CTAs measured slower in both directions.)
+// with CW = 32 to double the CTA count.  (512-thread CTAs measured slower in both directions; backward
+// shapes with 4 rows per slot at 3 CTAs per SM, 78 registers, measured 264-266 us inside the step against
+// 254 us for the 8-row shape at 2 CTAs per SM.)
 static int pick_cfg(int B, int D, bool backward) {
+  if (backward)
+    if (const char* e = getenv("HAWK_SCAN_CFG_BWD")) return atoi(e);  // tuning/debug override, backward only
   if (const char* e = getenv("HAWK_SCAN_CFG")) return atoi(e);  // tuning/debug override
   const bool many = (int64_t)B * (D / 64) >= 200;
   if (!backward) return many ? 3 : 6;
