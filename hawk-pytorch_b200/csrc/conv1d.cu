@@ -178,18 +178,39 @@ conv1d_bwd_kernel(const TG* __restrict__ go, const TX* __restrict__ x, int64_t x
         float out[VEC], xin[VEC], gin[VEC];
         RawVec<TX, VEC>::unpack(xraw[u], xin);
         RawVec<TG, VEC>::unpack(graw[u], gin);
-#pragma unroll
-        for (int v = 0; v < VEC; ++v) {
-          xw[0][v] = xin[v];
-          gw[W - 1][v] = gin[v];
-          float s = 0.f;
+        if constexpr (VEC == 2) {
+          // the thread's two channels as one packed fp32x2 operand: half the FMA-pipe instructions
+          xw[0][0] = xin[0]; xw[0][1] = xin[1];
+          gw[W - 1][0] = gin[0]; gw[W - 1][1] = gin[1];
+          const float2 g0 = make_float2(gw[0][0], gw[0][1]);
+          float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
           for (int k = 0; k < W; ++k) {
-            s = fmaf(wv[W - 1 - k][v], gw[k][v], s);                          // dx
-            acc[W - 1 - k][v] = fmaf(gw[0][v], xw[k][v], acc[W - 1 - k][v]);  // dw
+            s2 = fma2(make_float2(wv[W - 1 - k][0], wv[W - 1 - k][1]), make_float2(gw[k][0], gw[k][1]), s2);  // dx
+            const float2 a2 = fma2(g0, make_float2(xw[k][0], xw[k][1]),
+                                   make_float2(acc[W - 1 - k][0], acc[W - 1 - k][1]));                        // dw
+            acc[W - 1 - k][0] = a2.x;
+            acc[W - 1 - k][1] = a2.y;
           }
-          acc[W][v] += gw[0][v];  // dbias
-          out[v] = s;
+          const float2 b2 = add2(make_float2(acc[W][0], acc[W][1]), g0);  // dbias
+          acc[W][0] = b2.x;
+          acc[W][1] = b2.y;
+          out[0] = s2.x;
+          out[1] = s2.y;
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            xw[0][v] = xin[v];
+            gw[W - 1][v] = gin[v];
+            float s = 0.f;
+#pragma unroll
+            for (int k = 0; k < W; ++k) {
+              s = fmaf(wv[W - 1 - k][v], gw[k][v], s);                          // dx
+              acc[W - 1 - k][v] = fmaf(gw[0][v], xw[k][v], acc[W - 1 - k][v]);  // dw
+            }
+            acc[W][v] += gw[0][v];  // dbias
+            out[v] = s;
+          }
         }
         VecIO<TX, VEC>::store(dxrow + (int64_t)u * dxrs, out);
 #pragma unroll
