@@ -217,3 +217,47 @@ def test_scan_metric_shape_properties():
     for a, b in zip((xs[0].grad, xs[1].grad, xs[2].grad), (wdx, wdgx, wdga)):
         assert rel_l2(a[:2][..., idx.cuda()].float().cpu(), b) <= BF16_TOL
     assert torch.isfinite(lam_r.grad).all()
+
+
+def test_scan_long_sequence_shape_properties():
+    """B=1, T=65536, D=4096 bf16 (the long-sequence stress shape; 268 M elements): (1) time-locality over a
+    prefix that ends inside a super-step; (2) a 64-channel slice scanned alone gives the same bits in the
+    forward; (3) sampled channels match the fp64 oracle over all 65536 steps, forward and backward, with
+    gate biases inside the kernel."""
+    from hawk_b200 import fused_linear_scan
+    B, T, D = 1, 65536, 4096
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x, gx, ga, go = (torch.randn(B, T, D, generator=g, device="cuda").bfloat16() for _ in range(4))
+    lam = oscan.rnn_param_ring(D, generator=torch.Generator().manual_seed(4)).cuda()
+    gb = 0.3 * torch.randn(2, D, generator=g, device="cuda")
+    xs = [t.clone().requires_grad_(True) for t in (x, gx, ga)]
+    lam_r, gb_r = lam.clone().requires_grad_(True), gb.clone().requires_grad_(True)
+    h = fused_linear_scan(*xs, lam_r, gate_bias=gb_r)
+    h.backward(go)
+    assert bool(torch.isfinite(h).all())
+    # (1)
+    tcut = 40001
+    h_pre = fused_linear_scan(x[:, :tcut].contiguous(), gx[:, :tcut].contiguous(), ga[:, :tcut].contiguous(), lam,
+                              gate_bias=gb)
+    assert torch.equal(h_pre, h.detach()[:, :tcut])
+    # (2)
+    sl = slice(2048, 2112)
+    h_sl = fused_linear_scan(x[..., sl].contiguous(), gx[..., sl].contiguous(), ga[..., sl].contiguous(),
+                             lam[sl].contiguous(), gate_bias=gb[:, sl].contiguous())
+    assert torch.equal(h_sl, h.detach()[..., sl])
+    # (3)
+    idx = torch.tensor([0, 65, 2047, 4095])
+    ic = idx.cuda()
+    cx, cgx, cga, cgo = (t[..., ic].float().cpu() for t in (x, gx, ga, go))
+    cgb = gb[:, ic].cpu()
+    cgx, cga = cgx + cgb[0], cga + cgb[1]
+    hs = h.detach()[..., ic].float().cpu()
+    lam_c = lam.cpu()[idx]
+    want_h = oscan.rglru_scan_fwd(cx, cgx, cga, lam_c, compute=torch.float64)
+    assert rel_l2(hs, want_h) <= BF16_TOL
+    wdx, wdgx, wdga, wdlam = oscan.rglru_scan_bwd(cx, cgx, cga, lam_c, hs.double(), cgo, compute=torch.float64)
+    for a, b in zip((xs[0].grad, xs[1].grad, xs[2].grad), (wdx, wdgx, wdga)):
+        assert rel_l2(a[..., ic].float().cpu(), b) <= BF16_TOL
+    assert rel_l2(lam_r.grad[ic].cpu(), wdlam) <= BF16_TOL
+    want_gb = torch.stack((wdgx.sum((0, 1)), wdga.sum((0, 1))))
+    assert rel_l2(gb_r.grad[:, ic].cpu(), want_gb) <= BF16_TOL
