@@ -847,18 +847,6 @@ def linear(x, w, w_bf16=None):
     return F.linear(x, w)
 
 
-def adamw_step_(p, g, m, v, p_bf16, lr, beta1, beta2, eps, weight_decay, step):
-    """In-place AdamW update of one fp32 tensor through the C ABI (see hawk_adamw_step); called by
-    `train.FusedAdamW` under no_grad, outside any graph capture or compilation."""
-    lib = _lib.load()
-    assert p.is_cuda and p.dtype == g.dtype == m.dtype == v.dtype == torch.float32
-    assert p.is_contiguous() and g.is_contiguous() and m.is_contiguous() and v.is_contiguous()
-    assert p_bf16 is None or (p_bf16.dtype == torch.bfloat16 and p_bf16.is_contiguous() and p_bf16.shape == p.shape)
-    with _on(p, "adamw_step", 1):
-        _lib.check(lib.hawk_adamw_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _ptr(p_bf16), p.numel(),
-                                       lr, beta1, beta2, eps, weight_decay, step, _stream(p)), "hawk_adamw_step")
-
-
 # ---------------------------------------------------------------------------------------------
 # the recurrent branch between its two projections as one autograd node
 # ---------------------------------------------------------------------------------------------
