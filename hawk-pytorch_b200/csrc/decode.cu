@@ -180,24 +180,25 @@ decode_block_step_kernel(const T* __restrict__ xy, int64_t ld_xy, TS* __restrict
     const int gate = o / bw, j = o - gate * bw;
     const TW* wp = ws + (size_t)gate * bw * bw + j;
     const float bias = (gate ? ba : bx)[ch0 + j];
-    float acc[kDecTB];
+    float2 acc[kDecTB / 2];  // batch rows in pairs: packed fp32x2 FMAs, same rounding as scalar ones
 #pragma unroll
-    for (int b = 0; b < kDecTB; ++b) acc[b] = bias;
+    for (int b = 0; b < kDecTB / 2; ++b) acc[b] = f2(bias);
 #pragma unroll 4
     for (int k = 0; k < bw; ++k) {
-      const float wv = to_float(wp[k * bw]);
+      const float2 wv = f2(to_float(wp[k * bw]));
       const float4* xr = reinterpret_cast<const float4*>(xcT + k * kDecTB);
 #pragma unroll
       for (int q = 0; q < kDecTB / 4; ++q) {
         const float4 xv = xr[q];
-        acc[4 * q] = fmaf(xv.x, wv, acc[4 * q]);
-        acc[4 * q + 1] = fmaf(xv.y, wv, acc[4 * q + 1]);
-        acc[4 * q + 2] = fmaf(xv.z, wv, acc[4 * q + 2]);
-        acc[4 * q + 3] = fmaf(xv.w, wv, acc[4 * q + 3]);
+        acc[2 * q] = fma2(make_float2(xv.x, xv.y), wv, acc[2 * q]);
+        acc[2 * q + 1] = fma2(make_float2(xv.z, xv.w), wv, acc[2 * q + 1]);
       }
     }
 #pragma unroll
-    for (int b = 0; b < kDecTB; ++b) g[((size_t)gate * kDecTB + b) * bw + j] = acc[b];
+    for (int b = 0; b < kDecTB / 2; ++b) {
+      g[((size_t)gate * kDecTB + 2 * b) * bw + j] = acc[b].x;
+      g[((size_t)gate * kDecTB + 2 * b + 1) * bw + j] = acc[b].y;
+    }
   }
   __syncthreads();
 
