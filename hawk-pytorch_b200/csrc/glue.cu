@@ -26,7 +26,8 @@ __device__ __forceinline__ void gelu_and_grad(float x, float& g, float& dg) {
 // for every a^2 (also far outside the fitted range), so the form saturates to 0 / a by itself: no
 // clamps and no branches.  Evaluated on the channel pair with packed fp32x2 operations and two MUFU
 // operations per element (2^x and the reciprocal).
-// Coefficients of -log2(e) q(s), highest degree first (derived by fit_gelu_logit.py beside this file).
+// Coefficients of -log2(e) q(s), highest degree first: a Lawson-weighted least-squares (near-minimax) fit
+// of q over a^2 <= 30.25 (tests/golden/fit_gelu_logit.py reproduces them; not needed at run time).
 __device__ __forceinline__ void gelu_pair_fast(float2 a, float2& phi, float2& g) {
   const float2 s = mul2(a, a);
   float2 q = fma2(s, f2(-5.2099971e-09f), f2(3.8504896e-07f));

@@ -53,11 +53,14 @@ class KernelLog:
     def __init__(self):
         self.enabled = False
         self.timed = False
+        self.only = None
         self.counts = {}
         self.events = {}
 
-    def reset(self, enabled: bool = True, timed: bool = False) -> None:
+    def reset(self, enabled: bool = True, timed: bool = False, only=None) -> None:
+        """`only`: names of the entry points to bracket with events (None = all); counting covers all."""
         self.enabled, self.timed = enabled, timed
+        self.only = None if only is None else frozenset(only)
         self.counts, self.events = {}, {}
 
     def total_launches(self) -> int:
@@ -94,7 +97,7 @@ class _on:
             torch.cuda.set_device(self.idx)
         if LOG.enabled and self.name:
             LOG.counts[self.name] = LOG.counts.get(self.name, 0) + self.kernels
-            if LOG.timed:
+            if LOG.timed and (LOG.only is None or self.name in LOG.only):
                 self.stream = torch.cuda.current_stream()
                 self.start = torch.cuda.Event(enable_timing=True)
                 self.start.record(self.stream)
@@ -111,6 +114,11 @@ class _on:
 # ---------------------------------------------------------------------------------------------
 # RG-LRU scan
 # ---------------------------------------------------------------------------------------------
+# bytes each entry point must move per [B,T,D] element with bf16 storage (its HBM roofline), and the
+# pair of entry points the model's training step launches for the scan
+SCAN_BYTES_PER_ELEMENT = {"scan_fwd": 8, "scan_bwd": 16}
+SCAN_ENTRY_POINTS = ("scan_fwd", "scan_bwd")
+
 @torch.library.custom_op("hawk_b200::scan_fwd", mutates_args=())
 def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
              h0: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:

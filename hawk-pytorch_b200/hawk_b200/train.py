@@ -135,8 +135,7 @@ class Trainer:
             from torch.nn.parallel import DistributedDataParallel as DDP
             ids = [self.device.index] if self.device.type == "cuda" else None
             self.ddp = DDP(self.model, device_ids=ids, gradient_as_bucket_view=True, bucket_cap_mb=bucket_cap_mb)
-        # HAWK_B200_OPTIMIZER=torch selects torch.optim.AdamW(fused=True) instead (for A/B timing)
-        if self.device.type == "cuda" and os.environ.get("HAWK_B200_OPTIMIZER", "fused") != "torch":
+        if self.device.type == "cuda":
             from .model import Linear
             shadows = [m for m in self.model.modules() if isinstance(m, Linear) and m.bias is None] if self.autocast else []
             self.opt = FusedAdamW(self.model.parameters(), lr=lr, weight_decay=0.1, shadow_modules=shadows)
@@ -144,11 +143,15 @@ class Trainer:
             self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.1,
                                          fused=self.device.type == "cuda")
 
-    def step(self, ids: torch.Tensor) -> torch.Tensor:
+    def step(self, ids: torch.Tensor, after_backward=None) -> torch.Tensor:
+        """One training step; `after_backward(loss)`, when given, runs between the backward pass (gradients
+        all-reduced) and the optimiser update, e.g. to inspect gradients."""
         net = self.ddp if self.ddp is not None else self.model
         with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast):
             loss = net(ids, ids)
         loss.backward()
+        if after_backward is not None:
+            after_backward(loss.detach())
         self.opt.step()
         self.opt.zero_grad(set_to_none=True)
         return loss.detach()

@@ -64,8 +64,9 @@ const char* hawk_strerror(int status);
  * fixed at zero, scan_fused.py:77-79); pass NULL for the reference behaviour.
  * gate_bias / dgate_bias: optional [2,D] fp32, row 0 for gx and row 1 for ga.  With gate_bias the
  * gates are sigmoid(gx + gate_bias[0]) and sigmoid(ga + gate_bias[1]): the bias add of the
- * reference's block-diagonal gate projections (BlockDiagonalLinear, hawk/hawk.py:41-45, applied at
- * :128-129) done inside the scan, with the sum rounded to `dtype` as the reference's add is.  The
+ * reference's block-diagonal gate projections (BlockDiagonalLinear, hawk/external.py:171-233, the add at
+ * :230; called at hawk/hawk.py:181-182) done inside the scan.  The sum is kept in fp32 (the reference
+ * rounds gate + bias to bf16 under autocast before its scan, hawk/scan_fused.py:428).  The
  * caller then passes the bias-free projections as gx, ga.  dgate_bias receives the sums of dgx and
  * dga over batch and time (what autograd's bias gradient computes), in fp32, in a fixed order.
  * Pass NULL for the reference's scan signature.

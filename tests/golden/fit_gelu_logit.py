@@ -1,4 +1,4 @@
-"""Derives the coefficients of `gelu_pair_fast` in glue.cu (needs numpy and scipy; not used at run time).
+"""Derives the coefficients of `gelu_pair_fast` in hawk-pytorch_b200/csrc/glue.cu (needs numpy and scipy; not used at run time).
 
 The bf16 GELU kernels evaluate the exact (erf) GELU as a * Phi(a) with Phi(a) = 1 / (1 + exp(-a q(a^2))),
 where a q(a^2) = log(Phi(a) / Phi(-a)) exactly.  q is smooth and grows slowly, so a low-degree polynomial
@@ -7,7 +7,7 @@ fit), weighting by the sensitivity of a * Phi(a) to an error in q, and prints th
 -log2(e) * q(s), highest degree first, as the kernel's Horner chain uses them, together with the error
 of the fp32 evaluation over |a| <= 60 and at the largest magnitudes.
 
-    python hawk-pytorch_b200/csrc/fit_gelu_logit.py
+    python tests/golden/fit_gelu_logit.py
 """
 import numpy as np
 from scipy.special import log_ndtr, ndtr

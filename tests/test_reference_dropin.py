@@ -1,5 +1,5 @@
-"""Drop-in check against the real reference package, when a checkout of it sits next to this
-repository (skipped otherwise): install() rebinds the three operator names inside hawk/hawk.py and
+"""Drop-in check against the real reference package, staged by `python oracle/make_ref.py` into
+oracle/_ref (skipped when absent): install() rebinds the three operator names inside hawk/hawk.py and
 the reference's own HawkModel then runs through them with its own call conventions (keyword `x=` for
 the conv, positional scan arguments, `.view`-ed cross-entropy inputs) and reproduces the fixture.
 CPU only: the operators are substituted by their oracle statements BEFORE install() binds them, so
@@ -11,17 +11,15 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from conftest import ROOT, load_golden, max_rel
+from conftest import load_golden, max_rel
+from oracle import make_ref
 from oracle import model as omodel
 
-REF = os.path.join(os.path.dirname(ROOT), "reference")
 
-
-@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "hawk")), reason="no reference checkout next to the repo")
+@pytest.mark.skipif(not make_ref.available(), reason="reference not staged (python oracle/make_ref.py <checkout>)")
 def test_reference_model_runs_on_the_rebound_operators(monkeypatch):
     os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
-    monkeypatch.syspath_prepend(REF)
-    import hawk  # the reference package
+    hawk = make_ref.load()  # the reference package
     from hawk_b200 import install, ops
 
     class OracleConv1D(ops.Conv1D):  # same parameters and constructor; CPU statement of the forward
