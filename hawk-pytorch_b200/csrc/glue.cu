@@ -9,51 +9,6 @@
 
 namespace hawk {
 
-// exact (erf) GELU, as torch.nn.functional.gelu's default.  fp32 storage evaluates it with erff.
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ void gelu_and_grad(float x, float& g, float& dg) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  g = x * cdf;
-  dg = cdf + x * pdf;
-}
-
-// bf16 storage: the erff form costs ~30 instructions per element, which makes these kernels issue
-// bound, not HBM bound.  The same function in logistic form: Phi(a) = 1 / (1 + exp(-a q(a^2))), where
-// a q(a^2) = log(Phi(a) / Phi(-a)) exactly; q is smooth, and its degree-6 least-maximum fit (in a^2,
-// weighted by the sensitivity of a Phi(a)) leaves |gelu error| < 7e-7 and a relative error < 7e-4 in
-// the negative tail, two to three orders below the bf16 rounding of the result.  q > 1.59 and grows
-// for every a^2 (also far outside the fitted range), so the form saturates to 0 / a by itself: no
-// clamps and no branches.  Evaluated on the channel pair with packed fp32x2 operations and two MUFU
-// operations per element (2^x and the reciprocal).
-// Coefficients of -log2(e) q(s), highest degree first: a Lawson-weighted least-squares (near-minimax) fit
-// of q over a^2 <= 30.25 (tests/golden/fit_gelu_logit.py reproduces them; not needed at run time).
-__device__ __forceinline__ void gelu_pair_fast(float2 a, float2& phi, float2& g) {
-  const float2 s = mul2(a, a);
-  float2 q = fma2(s, f2(-5.2099971e-09f), f2(3.8504896e-07f));
-  q = fma2(q, s, f2(-1.1452494e-05f));
-  q = fma2(q, s, f2(1.5938988e-04f));
-  q = fma2(q, s, f2(9.5591375e-05f));
-  q = fma2(q, s, f2(-1.0483858e-01f));
-  q = fma2(q, s, f2(-2.3022072e+00f));
-  float2 e = mul2(a, q);
-  e.x = ex2_approx(e.x);  // +inf for very negative a: the reciprocal is then 0
-  e.y = ex2_approx(e.y);
-  const float2 d = add2(e, f2(1.f));
-  phi.x = rcp_approx(d.x);
-  phi.y = rcp_approx(d.y);
-  g = mul2(a, phi);
-}
-// and the derivative Phi(a) + a pdf(a), pdf(a) = exp(-a^2 / 2) / sqrt(2 pi)
-__device__ __forceinline__ void gelu_pair_fast_grad(float2 a, float2& g, float2& dg) {
-  float2 phi;
-  gelu_pair_fast(a, phi, g);
-  float2 p = mul2(mul2(a, a), f2(-0.72134752044448171f));  // -log2(e) / 2
-  p.x = ex2_approx(p.x);
-  p.y = ex2_approx(p.y);
-  dg = fma2(mul2(a, f2(0.3989422804014327f)), p, phi);
-}
-
 // VEC = 8 adjacent elements: out = gelu(a) * b
 template <typename T>
 struct GeluVec {

@@ -18,7 +18,12 @@
 // The backward is the same skeleton run from t = T-1 down, on the carried quantity
 // c_t = a_t * dh_t:   dh_t = go_t + c_{t+1},   c_t = a_t * dh_t,
 // which only needs row-local coefficients.  All outputs are dh_t times row-local factors.
-#include <cstdlib>
+//
+// GELU = true fuses the block's epilogue out = gelu(y) * h (hawk/hawk.py:134-135, called at :201) into
+// both kernels: the forward also stages y (the strided other half of the input projection) and stores
+// out next to h; the backward takes d out in place of d h, forms d h = d out * gelu(y) in its first
+// phase and writes d y = d out * gelu'(y) * h_t (h_t recomputed from the stored h_{t-1}) next to the
+// other gradients.  The separate gelu(y) * h pass over [B,T,D] in each direction disappears.
 #include <mutex>
 #include <type_traits>
 
@@ -35,22 +40,49 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-#ifndef HAWK_SCAN_BWD_EXP_GATES
-#define HAWK_SCAN_BWD_EXP_GATES 1  // backward gates from 2^x + shared reciprocal (1) or tanh (0)
-#endif
-
 template <typename T>
 struct SmemPair;  // two adjacent channels read back from the staging ring
 template <>
 struct SmemPair<float> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
+  // writes the pair back in storage precision and returns what a later ld() will read
+  static __device__ __forceinline__ float2 st(unsigned char* p, float2 v) {
+    *reinterpret_cast<float2*>(p) = v;
+    return v;
+  }
 };
 template <>
 struct SmemPair<__nv_bfloat16> {
   static __device__ __forceinline__ float2 ld(const unsigned char* p) {
     return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
   }
+  static __device__ __forceinline__ float2 st(unsigned char* p, float2 v) {
+    const uint32_t w = pack_bf16x2(v.x, v.y);
+    *reinterpret_cast<uint32_t*>(p) = w;
+    return unpack_bf16x2(w);
+  }
 };
+
+// gelu(y) and its derivative for the lane's channel pair: logistic form on the bf16 path (two / three MUFU
+// operations per element), erff for fp32 storage
+template <bool FAST>
+__device__ __forceinline__ float2 gelu2(float2 y) {
+  if (FAST) {
+    float2 phi, g;
+    gelu_pair_fast(y, phi, g);
+    return g;
+  }
+  return make_float2(gelu_f(y.x), gelu_f(y.y));
+}
+template <bool FAST>
+__device__ __forceinline__ void gelu2_grad(float2 y, float2& g, float2& dg) {
+  if (FAST) {
+    gelu_pair_fast_grad(y, g, dg);
+  } else {
+    gelu_and_grad(y.x, g.x, dg.x);
+    gelu_and_grad(y.y, g.y, dg.y);
+  }
+}
 
 template <bool FAST>
 __device__ __forceinline__ float gate_scale(float lam) {
@@ -243,12 +275,14 @@ struct Geo {
 // ----------------------------------------------------------------------------------------------
 // forward
 // ----------------------------------------------------------------------------------------------
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
+// GELU: y is the [B,T,D] view with strides (y_bs, y_ld) elements; out = gelu(y) * h is [B,T,D] contiguous.
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
                 const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
-                T* __restrict__ h, int T_len, int D) {
-  using G = Geo<T, R, WARPS, LPR, 3>;
+                T* __restrict__ h, int T_len, int D, const T* __restrict__ y, size_t y_bs, uint32_t y_ld,
+                T* __restrict__ out) {
+  using G = Geo<T, R, WARPS, LPR, GELU ? 4 : 3>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float4 carry[2][WARPS][LPR];     // (P.x, P.y, hl.x, hl.y) of each warp's rows
@@ -278,6 +312,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   unsigned char* ring = smem + (size_t)warp * STAGES * G::STAGE_BYTES;
   const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
   const T* src[3] = {x + base + ch0, gx + base + ch0, ga + base + ch0};
+  const T* ysrc = GELU ? y + (size_t)b * y_bs + ch0 : nullptr;
   const int nsteps = (T_len + G::ROWS - 1) / G::ROWS;
   const int nfull = T_len / G::ROWS;  // super-steps with every row inside the sequence
   const uint32_t uD = (uint32_t)D;
@@ -285,18 +320,22 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   // warp-private copy of this warp's NR rows of super-step s into ring buffer s % STAGES.
   // Staged row m holds time row (m % NSUB) * R + m / NSUB of the warp, so that the slots of a warp
   // read adjacent shared-memory rows (no bank conflicts).  Element offsets fit 32 bits (host check).
-  uint32_t cp_off[G::NCP];  // element offset of this lane's c-th copy within super-step 0
+  uint32_t cp_off[G::NCP];   // element offset of this lane's c-th copy within super-step 0
+  uint32_t cp_offy[G::NCP];  // the same in y's row pitch
 #pragma unroll
   for (int c = 0; c < G::NCP; ++c) {
     const int m = c * G::RPI + lane / G::CPR;
-    cp_off[c] = (uint32_t)(warp * G::NR + (m % G::NSUB) * R + m / G::NSUB) * uD +
-                (uint32_t)(lane % G::CPR) * (16 / sizeof(T));
+    const uint32_t row = (uint32_t)(warp * G::NR + (m % G::NSUB) * R + m / G::NSUB);
+    const uint32_t col = (uint32_t)(lane % G::CPR) * (16 / sizeof(T));
+    cp_off[c] = row * uD + col;
+    cp_offy[c] = GELU ? row * y_ld + col : 0u;
   }
   const uint32_t cp_dst = ring_addr + (uint32_t)((lane / G::CPR) * G::ROWB + (lane % G::CPR) * 16);
   auto issue = [&](int s) {
     if (s < nsteps) {
       const uint32_t dst0 = cp_dst + (uint32_t)((s & (STAGES - 1)) * G::STAGE_BYTES);
       const uint32_t step_off = (uint32_t)s * (uint32_t)G::ROWS * uD;
+      const uint32_t step_offy = GELU ? (uint32_t)s * (uint32_t)G::ROWS * y_ld : 0u;
       const bool full = s < nfull;
 #pragma unroll
       for (int c = 0; c < G::NCP; ++c) {
@@ -306,6 +345,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
           const uint32_t o = step_off + cp_off[c];
 #pragma unroll
           for (int q = 0; q < 3; ++q) cp_async16(dst0 + c * G::RPI * G::ROWB + q * G::IN_BYTES, src[q] + o);
+          if (GELU) cp_async16(dst0 + c * G::RPI * G::ROWB + 3 * G::IN_BYTES, ysrc + (step_offy + cp_offy[c]));
         }
       }
     }
@@ -316,6 +356,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
   T* hp = h + base + ch;
+  T* outp = GELU ? out + base + ch : nullptr;
   // One super-step.  FULL = every row is inside the sequence: no per-row predicates.
   auto step = [&](int s, auto full_tag) {
     constexpr bool FULL = decltype(full_tag)::value;
@@ -363,7 +404,18 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       hin = fma2(a[r], hin, be[r]);
-      if (FULL || t0 + r < T_len) P_::store(hp + (o0 + (uint32_t)r * uD), hin.x, hin.y);
+      if (FULL || t0 + r < T_len) {
+        if (GELU) {
+          // out = gelu(y) * h with h as stored (what a separate pass would have read back)
+          const typename P_::raw hs = P_::pack(hin.x, hin.y);
+          P_::store_raw(hp + (o0 + (uint32_t)r * uD), hs);
+          const float2 g = gelu2<FAST>(SmemPair<T>::ld(st + r * G::NSUB * G::ROWB + 3 * G::IN_BYTES));
+          const float2 o = mul2(g, P_::unpack(hs));
+          P_::store(outp + (o0 + (uint32_t)r * uD), o.x, o.y);
+        } else {
+          P_::store(hp + (o0 + (uint32_t)r * uD), hin.x, hin.y);
+        }
+      }
     }
   };
 
@@ -375,14 +427,16 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 // ----------------------------------------------------------------------------------------------
 // backward
 // ----------------------------------------------------------------------------------------------
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
+// GELU: `go` is d out; y and dy are [B,T,D] views with strides (y_bs, y_ld) / (dy_bs, dy_ld) elements.
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
                 const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
                 const T* __restrict__ h, const T* __restrict__ go, T* __restrict__ dx, T* __restrict__ dgx,
                 T* __restrict__ dga, float* __restrict__ dlam_partial, float* __restrict__ dgb_partial,
-                float* __restrict__ dh0, int T_len, int D, int B_total) {
-  using G = Geo<T, R, WARPS, LPR, 5>;
+                float* __restrict__ dh0, int T_len, int D, int B_total, const T* __restrict__ y, size_t y_bs,
+                uint32_t y_ld, T* __restrict__ dy, size_t dy_bs, uint32_t dy_ld) {
+  using G = Geo<T, R, WARPS, LPR, GELU ? 6 : 5>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float4 carry[2][WARPS][LPR];
@@ -415,8 +469,12 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   static_assert((STAGES & (STAGES - 1)) == 0, "STAGES must be a power of two");
   unsigned char* ring = smem + (size_t)warp * STAGES * G::STAGE_BYTES;
   const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
-  // staged inputs: 0 = ga, 1 = go, 2 = x, 3 = gx, 4 = h shifted by one row (h_{t-1})
+  // staged inputs: 0 = ga, 1 = go, 2 = x, 3 = gx, 4 = h shifted by one row (h_{t-1}), 5 = y (GELU only).
+  // With GELU the first phase overwrites slot 1 with d h = d out * gelu(y) and slot 5 with d out * gelu'(y),
+  // rounded to the storage type (as the tensors of a separate gelu pass would be); each lane rewrites only
+  // the (row, channel pair) entries it alone reads.
   const T* src[5] = {ga + base + ch0, go + base + ch0, x + base + ch0, gx + base + ch0, h + base + ch0};
+  const T* ysrc = GELU ? y + (size_t)b * y_bs + ch0 : nullptr;
   const int nsteps = (T_len + G::ROWS - 1) / G::ROWS;
   const int nfull = T_len / G::ROWS;
   const uint32_t uD = (uint32_t)D;
@@ -444,6 +502,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 #pragma unroll
           for (int q = 0; q < 4; ++q) cp_async16(d + q * G::IN_BYTES, src[q] + o);
           if (t > 0) cp_async16(d + 4 * G::IN_BYTES, src[4] + (o - uD));
+          if (GELU) cp_async16(d + 5 * G::IN_BYTES, ysrc + ((uint32_t)t * y_ld + cp_col));
         }
       }
     }
@@ -458,6 +517,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   T* dxp = dx + base + ch;
   T* dgxp = dgx + base + ch;
   T* dgap = dga + base + ch;
+  T* dyp = GELU ? dy + (size_t)b * dy_bs + ch : nullptr;
 
   // One super-step.  FULL = every row is inside the sequence and none is t = 0.
   auto step = [&](int s, auto full_tag) {
@@ -467,8 +527,8 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     cp_async_wait<STAGES - 1>();
     __syncwarp();
 
-    const unsigned char* st = ring + (size_t)(s & (STAGES - 1)) * G::STAGE_BYTES +
-                              (size_t)(sub * G::ROWB + cl * 2 * (int)sizeof(T));
+    unsigned char* st = ring + (size_t)(s & (STAGES - 1)) * G::STAGE_BYTES +
+                        (size_t)(sub * G::ROWB + cl * 2 * (int)sizeof(T));
     const int tt = T_len - 1 - (s * G::ROWS + slot * R);  // time of this slot's first (latest) row
 
     // phase 1: a_t, both gates and the chunk summary of c <- a * (go + c)
@@ -478,9 +538,15 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     for (int r = 0; r < R; ++r) {
       float2 gov = f2(0.f);
       if (FULL || tt - r >= 0) {
-        const unsigned char* row = st + r * G::NSUB * G::ROWB;
+        unsigned char* row = st + r * G::NSUB * G::ROWB;
         gov = SmemPair<T>::ld(row + G::IN_BYTES);
-        if (FAST && HAWK_SCAN_BWD_EXP_GATES)
+        if (GELU) {
+          float2 g, dg;
+          gelu2_grad<FAST>(SmemPair<T>::ld(row + 5 * G::IN_BYTES), g, dg);
+          SmemPair<T>::st(row + 5 * G::IN_BYTES, mul2(gov, dg));
+          gov = SmemPair<T>::st(row + G::IN_BYTES, mul2(gov, g));
+        }
+        if (FAST)
           gates2_exp(ld_floored_bf16x2(row + 3 * G::IN_BYTES, fgx), ld_floored_bf16x2(row, fga), egx, ega, ig[r], rg[r]);
         else
           gates2<FAST>(SmemPair<T>::ld(row + 3 * G::IN_BYTES), SmemPair<T>::ld(row), bgx, bga, ig[r], rg[r]);
@@ -538,10 +604,15 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
         o_dgx = mul2(mul2(dm, xi), add2(f2(1.f), neg2(iv)));       // :242
         o_dga = mul2(mul2(mul2(rv, add2(f2(1.f), neg2(rv))), dla), q2);  // :254
         acc = fma2(dla, rv, acc);
+        if (GELU) {  // d y = (d out gelu'(y)) * h_t,  h_t = a h_{t-1} + x i m
+          const float2 ht = fma2(av, hpv, mul2(xi, m));
+          const float2 o_dy = mul2(SmemPair<T>::ld(row + 5 * G::IN_BYTES), ht);
+          P_::store(dyp + (uint32_t)t * dy_ld, o_dy.x, o_dy.y);
+        }
       } else {
         float* pc = &c.x;  // silence unused warnings in this branch
         (void)pc;
-        float dxs[2], dgxs[2], dgas[2];
+        float dxs[2], dgxs[2], dgas[2], hts[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const float x_e = e ? xv.y : xv.x, hp_e = e ? hpv.y : hpv.x, dh_e = e ? dh.y : dh.x;
@@ -557,6 +628,11 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
           dgxs[e] = dm * xi * (1.f - i_e);
           dgas[e] = (r_e * (1.f - r_e)) * dla * (e ? q2.y : q2.x);
           if (e) acc.y = fmaf(dla, r_e, acc.y); else acc.x = fmaf(dla, r_e, acc.x);
+          hts[e] = fmaf(a_e, hp_e, xi * m);
+        }
+        if (GELU) {
+          const float2 dd = SmemPair<T>::ld(row + 5 * G::IN_BYTES);
+          P_::store(dyp + (uint32_t)t * dy_ld, dd.x * hts[0], dd.y * hts[1]);
         }
         o_dx = make_float2(dxs[0], dxs[1]);
         o_dgx = make_float2(dgxs[0], dgxs[1]);
@@ -630,11 +706,21 @@ __global__ void scan_dlam_reduce_kernel(const float* __restrict__ partial, float
 }
 
 // ---- launch ---------------------------------------------------------------------------------
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
+struct GeluArgs {  // the fused gelu(y) * h epilogue: y / dy as [B,T,D] views (strides in elements), out contiguous
+  const void* y = nullptr;
+  size_t y_bs = 0;
+  uint32_t y_ld = 0;
+  void* out = nullptr;  // forward
+  void* dy = nullptr;   // backward
+  size_t dy_bs = 0;
+  uint32_t dy_ld = 0;
+};
+
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
 static int launch_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                      const float* gbias, void* h, int B, int T_len, int D, cudaStream_t st) {
-  using G = Geo<T, R, WARPS, LPR, 3>;
-  auto kern = scan_fwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST>;
+                      const float* gbias, void* h, int B, int T_len, int D, const GeluArgs& ge, cudaStream_t st) {
+  using G = Geo<T, R, WARPS, LPR, GELU ? 4 : 3>;
+  auto kern = scan_fwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -642,17 +728,18 @@ static int launch_fwd(const void* x, const void* gx, const void* ga, const float
   }
   kern<<<B * (D / G::CW), WARPS * 32, smem, st>>>(static_cast<const T*>(x), static_cast<const T*>(gx),
                                                    static_cast<const T*>(ga), lam, h0, gbias, static_cast<T*>(h),
-                                                   T_len, D);
+                                                   T_len, D, static_cast<const T*>(ge.y), ge.y_bs, ge.y_ld,
+                                                   static_cast<T*>(ge.out));
   return launch_status();
 }
 
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST>
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
 static int launch_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
                       const float* gbias, const void* h, const void* go, void* dx, void* dgx, void* dga,
                       float* dlam, float* dh0, float* dgbias, float* partial, int B, int T_len, int D,
-                      cudaStream_t st) {
-  using G = Geo<T, R, WARPS, LPR, 5>;
-  auto kern = scan_bwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST>;
+                      const GeluArgs& ge, cudaStream_t st) {
+  using G = Geo<T, R, WARPS, LPR, GELU ? 6 : 5>;
+  auto kern = scan_bwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -661,7 +748,8 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
   kern<<<B * (D / G::CW), WARPS * 32, smem, st>>>(
       static_cast<const T*>(x), static_cast<const T*>(gx), static_cast<const T*>(ga), lam, h0, gbias,
       static_cast<const T*>(h), static_cast<const T*>(go), static_cast<T*>(dx), static_cast<T*>(dgx),
-      static_cast<T*>(dga), partial, dgbias ? partial + (size_t)B * D : nullptr, dh0, T_len, D, B);
+      static_cast<T*>(dga), partial, dgbias ? partial + (size_t)B * D : nullptr, dh0, T_len, D, B,
+      static_cast<const T*>(ge.y), ge.y_bs, ge.y_ld, static_cast<T*>(ge.dy), ge.dy_bs, ge.dy_ld);
   int rc = launch_status();
   if (rc != HAWK_OK) return rc;
   const int nvec = dgbias ? 3 : 1;
@@ -677,15 +765,9 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
 // with CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
 // with CW = 32 to double the CTA count.  (512-thread CTAs measured slower in both directions; backward
 // shapes with 4 rows per slot at 3 CTAs per SM, 78 registers, measured 264-266 us inside the step against
-// 254 us for the 8-row shape at 2 CTAs per SM.)
-static int pick_cfg(int B, int D, bool backward) {
-  if (backward)
-    if (const char* e = getenv("HAWK_SCAN_CFG_BWD")) return atoi(e);  // tuning/debug override, backward only
-  if (const char* e = getenv("HAWK_SCAN_CFG")) return atoi(e);  // tuning/debug override
-  const bool many = (int64_t)B * (D / 64) >= 200;
-  if (!backward) return many ? 3 : 6;
-  return many ? 5 : 1;
-}
+// 254 us for the 8-row shape at 2 CTAs per SM.)  The fused-epilogue kernels stage one more input, so
+// their forward shapes hold one CTA fewer per SM (shared memory) or two stages instead of four.
+static bool many_groups(int B, int D) { return (int64_t)B * (D / 64) >= 200; }
 
 static int check_scan_common(int B, int T, int D, int dtype) {
   HAWK_REQUIRE(valid_dtype(dtype), HAWK_ERR_DTYPE);
@@ -693,6 +775,63 @@ static int check_scan_common(int B, int T, int D, int dtype) {
   HAWK_REQUIRE((int64_t)B * (D / 16) <= 0x7fffffffLL, HAWK_ERR_SHAPE);
   HAWK_REQUIRE((int64_t)(T + 1024) * D <= 0xffffffffLL, HAWK_ERR_SHAPE);  // 32-bit offsets within a batch row
   return HAWK_OK;
+}
+
+// a [B,T,D] view with element strides (bs, ld): rows of D contiguous elements, 16-byte aligned
+static int check_view(const void* p, int64_t bs, int64_t ld, int T, int D, int dtype, size_t align) {
+  HAWK_REQUIRE(p != nullptr, HAWK_ERR_NULL);
+  HAWK_REQUIRE(ld >= D && bs >= 0 && (int64_t)(T + 1024) * ld <= 0xffffffffLL, HAWK_ERR_SHAPE);
+  const int64_t per16 = 16 / (int64_t)dtype_size(dtype);
+  HAWK_REQUIRE(aligned(p, align) && ld % per16 == 0 && bs % per16 == 0, HAWK_ERR_ALIGN);
+  return HAWK_OK;
+}
+
+static int scan_fwd_dispatch(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                             const float* gate_bias, void* h, int B, int T, int D, int dtype, const GeluArgs* ge,
+                             cudaStream_t st) {
+  using bf = __nv_bfloat16;
+  const GeluArgs none;
+#define HAWK_FWD(TT, R, W, LPR, S, MINB, FAST, GELU) \
+  return launch_fwd<TT, R, W, LPR, S, MINB, FAST, GELU>(x, gx, ga, lam, h0, gate_bias, h, B, T, D, ge ? *ge : none, st)
+  const bool many = many_groups(B, D);
+  if (dtype == HAWK_BF16) {
+    if (ge) {
+      if (many) HAWK_FWD(bf, 8, 4, 8, 2, 6, true, true);
+      HAWK_FWD(bf, 8, 8, 8, 2, 3, true, true);
+    }
+    if (many) HAWK_FWD(bf, 8, 4, 8, 2, 7, true, false);
+    HAWK_FWD(bf, 8, 8, 8, 4, 2, true, false);
+  }
+  if (ge) HAWK_FWD(float, 4, 4, 8, 4, 3, false, true);
+  HAWK_FWD(float, 4, 4, 8, 4, 4, false, false);
+#undef HAWK_FWD
+}
+
+static int scan_bwd_dispatch(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                             const float* gate_bias, const void* h, const void* go, void* dx, void* dgx, void* dga,
+                             float* dlam, float* dh0, float* dgate_bias, float* partial, int B, int T, int D,
+                             int dtype, const GeluArgs* ge, cudaStream_t st) {
+  using bf = __nv_bfloat16;
+  const GeluArgs none;
+#define HAWK_BWD(TT, R, W, LPR, S, MINB, FAST, GELU)                                                                  \
+  return launch_bwd<TT, R, W, LPR, S, MINB, FAST, GELU>(x, gx, ga, lam, h0, gate_bias, h, go, dx, dgx, dga, dlam, dh0, \
+                                                        dgate_bias, partial, B, T, D, ge ? *ge : none, st)
+  const bool many = many_groups(B, D);
+  if (dtype == HAWK_BF16) {
+    if (ge) {
+      if (many) HAWK_BWD(bf, 8, 8, 32, 2, 2, true, true);
+      HAWK_BWD(bf, 4, 8, 16, 4, 2, true, true);
+    }
+    if (many) HAWK_BWD(bf, 8, 8, 32, 2, 2, true, false);
+    HAWK_BWD(bf, 4, 8, 16, 4, 2, true, false);
+  }
+  if (ge) {
+    if (many) HAWK_BWD(float, 2, 8, 32, 4, 2, false, true);
+    HAWK_BWD(float, 2, 8, 16, 4, 2, false, true);
+  }
+  if (many) HAWK_BWD(float, 2, 8, 32, 4, 2, false, false);
+  HAWK_BWD(float, 2, 8, 16, 4, 2, false, false);
+#undef HAWK_BWD
 }
 
 }  // namespace hawk
@@ -707,29 +846,26 @@ extern "C" int hawk_scan_fwd(const void* x, const void* gx, const void* ga, cons
   HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(lam, 8) &&
                    aligned(h0, 8) && aligned(gate_bias, 8),
                HAWK_ERR_ALIGN);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  using bf = __nv_bfloat16;
-#define HAWK_FWD(TT, R, W, LPR, S, MINB, FAST) \
-  return launch_fwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, gate_bias, h, B, T, D, st)
-  const int cfg = pick_cfg(B, D, false);
-  if (dtype == HAWK_BF16) {
-    switch (cfg) {
-      case 0: HAWK_FWD(bf, 8, 8, 32, 4, 2, true);
-      case 1: HAWK_FWD(bf, 8, 8, 16, 4, 2, true);
-      case 2: HAWK_FWD(bf, 8, 4, 16, 4, 4, true);
-      case 3: HAWK_FWD(bf, 8, 4, 8, 2, 7, true);
-      case 4: HAWK_FWD(bf, 8, 4, 8, 4, 4, true);
-      case 5: HAWK_FWD(bf, 4, 4, 8, 4, 7, true);
-      case 6: HAWK_FWD(bf, 8, 8, 8, 4, 2, true);
-      default: return HAWK_ERR_UNSUPPORTED;
-    }
-  }
-  switch (cfg) {
-    case 0: HAWK_FWD(float, 4, 8, 32, 4, 2, false);
-    case 1: case 2: HAWK_FWD(float, 4, 8, 16, 4, 2, false);
-    default: HAWK_FWD(float, 4, 4, 8, 4, 4, false);
-  }
-#undef HAWK_FWD
+  return scan_fwd_dispatch(x, gx, ga, lam, h0, gate_bias, h, B, T, D, dtype, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hawk_scan_gelu_fwd(const void* x, const void* gx, const void* ga, const float* lam,
+                                  const float* gate_bias, const void* y, int64_t y_batch_stride, int64_t y_row_stride,
+                                  void* h, void* out, int B, int T, int D, int dtype, void* stream) {
+  HAWK_REQUIRE(x && gx && ga && lam && h && out, HAWK_ERR_NULL);
+  int rc = check_scan_common(B, T, D, dtype);
+  if (rc != HAWK_OK) return rc;
+  rc = check_view(y, y_batch_stride, y_row_stride, T, D, dtype, 16);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(out, 16) &&
+                   aligned(lam, 8) && aligned(gate_bias, 8),
+               HAWK_ERR_ALIGN);
+  GeluArgs ge;
+  ge.y = y;
+  ge.y_bs = (size_t)y_batch_stride;
+  ge.y_ld = (uint32_t)y_row_stride;
+  ge.out = out;
+  return scan_fwd_dispatch(x, gx, ga, lam, nullptr, gate_bias, h, B, T, D, dtype, &ge, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t hawk_scan_bwd_workspace_bytes(int B, int D) {
@@ -751,31 +887,38 @@ extern "C" int hawk_scan_bwd(const void* x, const void* gx, const void* ga, cons
                    aligned(dx, 8) && aligned(dgx, 8) && aligned(dga, 8) && aligned(lam, 8) && aligned(h0, 8) &&
                    aligned(dh0, 8) && aligned(gate_bias, 8) && aligned(dgate_bias, 4) && aligned(workspace, 16),
                HAWK_ERR_ALIGN);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* partial = static_cast<float*>(workspace);
-  using bf = __nv_bfloat16;
-#define HAWK_BWD(TT, R, W, LPR, S, MINB, FAST)                                                                  \
-  return launch_bwd<TT, R, W, LPR, S, MINB, FAST>(x, gx, ga, lam, h0, gate_bias, h, go, dx, dgx, dga, dlam, dh0, \
-                                                  dgate_bias, partial, B, T, D, st)
-  const int cfg = pick_cfg(B, D, true);
-  if (dtype == HAWK_BF16) {
-    switch (cfg) {
-      case 0: HAWK_BWD(bf, 4, 8, 32, 4, 2, true);
-      case 1: HAWK_BWD(bf, 4, 8, 16, 4, 2, true);
-      case 2: HAWK_BWD(bf, 4, 4, 16, 4, 4, true);
-      case 3: HAWK_BWD(bf, 4, 4, 8, 2, 7, true);
-      case 4: HAWK_BWD(bf, 4, 4, 8, 4, 4, true);
-      case 5: HAWK_BWD(bf, 8, 8, 32, 2, 2, true);
-      default: return HAWK_ERR_UNSUPPORTED;
-    }
-  }
-  switch (cfg) {
-    case 0: HAWK_BWD(float, 2, 8, 32, 4, 2, false);
-    case 1: case 2: HAWK_BWD(float, 2, 8, 16, 4, 2, false);
-    case 5: HAWK_BWD(float, 2, 8, 32, 4, 2, false);
-    default: HAWK_BWD(float, 2, 4, 8, 4, 4, false);
-  }
-#undef HAWK_BWD
+  return scan_bwd_dispatch(x, gx, ga, lam, h0, gate_bias, h, go, dx, dgx, dga, dlam, dh0, dgate_bias,
+                           static_cast<float*>(workspace), B, T, D, dtype, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hawk_scan_gelu_bwd(const void* x, const void* gx, const void* ga, const float* lam,
+                                  const float* gate_bias, const void* h, const void* y, int64_t y_batch_stride,
+                                  int64_t y_row_stride, const void* dout, void* dx, void* dgx, void* dga, void* dy,
+                                  int64_t dy_batch_stride, int64_t dy_row_stride, float* dlam, float* dgate_bias,
+                                  void* workspace, size_t workspace_bytes, int B, int T, int D, int dtype,
+                                  void* stream) {
+  HAWK_REQUIRE(x && gx && ga && lam && h && dout && dx && dgx && dga && dlam, HAWK_ERR_NULL);
+  int rc = check_scan_common(B, T, D, dtype);
+  if (rc != HAWK_OK) return rc;
+  rc = check_view(y, y_batch_stride, y_row_stride, T, D, dtype, 16);
+  if (rc != HAWK_OK) return rc;
+  rc = check_view(dy, dy_batch_stride, dy_row_stride, T, D, dtype, 8);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(workspace && workspace_bytes >= (dgate_bias ? 3 : 1) * (size_t)B * (size_t)D * sizeof(float),
+               HAWK_ERR_WORKSPACE);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(dout, 16) &&
+                   aligned(dx, 8) && aligned(dgx, 8) && aligned(dga, 8) && aligned(lam, 8) && aligned(gate_bias, 8) &&
+                   aligned(dgate_bias, 4) && aligned(workspace, 16),
+               HAWK_ERR_ALIGN);
+  GeluArgs ge;
+  ge.y = y;
+  ge.y_bs = (size_t)y_batch_stride;
+  ge.y_ld = (uint32_t)y_row_stride;
+  ge.dy = dy;
+  ge.dy_bs = (size_t)dy_batch_stride;
+  ge.dy_ld = (uint32_t)dy_row_stride;
+  return scan_bwd_dispatch(x, gx, ga, lam, nullptr, gate_bias, h, dout, dx, dgx, dga, dlam, nullptr, dgate_bias,
+                           static_cast<float*>(workspace), B, T, D, dtype, &ge, static_cast<cudaStream_t>(stream));
 }
 
 // ----------------------------------------------------------------------------------------------

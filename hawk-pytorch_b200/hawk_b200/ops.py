@@ -116,8 +116,8 @@ class _on:
 # ---------------------------------------------------------------------------------------------
 # bytes each entry point must move per [B,T,D] element with bf16 storage (its HBM roofline), and the
 # pair of entry points the model's training step launches for the scan
-SCAN_BYTES_PER_ELEMENT = {"scan_fwd": 8, "scan_bwd": 16}
-SCAN_ENTRY_POINTS = ("scan_fwd", "scan_bwd")
+SCAN_BYTES_PER_ELEMENT = {"scan_fwd": 8, "scan_bwd": 16, "scan_gelu_fwd": 12, "scan_gelu_bwd": 20}
+SCAN_ENTRY_POINTS = ("scan_gelu_fwd", "scan_gelu_bwd")
 
 @torch.library.custom_op("hawk_b200::scan_fwd", mutates_args=())
 def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
@@ -219,14 +219,113 @@ def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None, gate_bias=None
     return scan_fwd(x, x_rg_lru, a_rg_lru, lam, h0, gate_bias)
 
 
-# ---------------------------------------------------------------------------------------------
-# temporal conv1d
-# ---------------------------------------------------------------------------------------------
 def _conv_view(x: torch.Tensor) -> torch.Tensor:
     """x as the kernels can read it in place: [B,T,D], unit channel stride, 16-byte aligned rows."""
     ok = (x.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
           and x.stride(1) >= x.shape[2])
     return x if ok else x.contiguous()
+
+
+# ---- the scan with the block's epilogue out = gelu(y) * h fused in (hawk/hawk.py:134-135,201) ----
+@torch.library.custom_op("hawk_b200::scan_gelu_fwd", mutates_args=())
+def scan_gelu_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
+                  gate_bias: Optional[torch.Tensor], y: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(h, gelu(y) * h); y [B,T,D] may be a row-strided view (the y half of the input projection)."""
+    lib = _lib.load()
+    B, T, D = x.shape
+    x, gx, ga, lam = x.contiguous(), gx.contiguous(), ga.contiguous(), lam.contiguous()
+    assert y.shape == x.shape and y.dtype == x.dtype
+    yv = _conv_view(y)
+    if gate_bias is not None:
+        assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
+        gate_bias = gate_bias.contiguous()
+    h, out = torch.empty_like(x), torch.empty_like(x)
+    with _on(x, "scan_gelu_fwd", 1):
+        _lib.check(lib.hawk_scan_gelu_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(gate_bias),
+                                          yv.data_ptr(), yv.stride(0), yv.stride(1), h.data_ptr(), out.data_ptr(),
+                                          B, T, D, _dt(x), _stream(x)), "hawk_scan_gelu_fwd")
+    return h, out
+
+
+@scan_gelu_fwd.register_fake
+def _(x, gx, ga, lam, gate_bias, y):
+    e = lambda: torch.empty_like(x, memory_format=torch.contiguous_format)
+    return e(), e()
+
+
+@torch.library.custom_op("hawk_b200::scan_gelu_bwd_into", mutates_args=("dy_out",))
+def scan_gelu_bwd_into(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
+                       gate_bias: Optional[torch.Tensor], h: torch.Tensor, y: torch.Tensor, dout: torch.Tensor,
+                       dy_out: torch.Tensor
+                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of scan_gelu_fwd from d out: returns (dx, dgx, dga, dlam, dgate_bias) and writes d y into
+    `dy_out`, a [B,T,D] view that may be row-strided (e.g. the y half of the projection's gradient)."""
+    lib = _lib.load()
+    B, T, D = x.shape
+    x, gx, ga, lam, h, dout = (t.contiguous() for t in (x, gx, ga, lam, h, dout))
+    if dout.dtype != x.dtype:
+        dout = dout.to(x.dtype)
+    yv = _conv_view(y)
+    assert dy_out.shape == x.shape and dy_out.dtype == x.dtype and _conv_view(dy_out) is dy_out
+    dx, dgx, dga = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    dlam = torch.empty(D, dtype=torch.float32, device=x.device)
+    dgb = torch.empty(2 if gate_bias is not None else 0, D, dtype=torch.float32, device=x.device)
+    ws_bytes = (3 if gate_bias is not None else 1) * B * D * 4
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    if gate_bias is not None:
+        gate_bias = gate_bias.contiguous()
+    with _on(x, "scan_gelu_bwd", 2):
+        _lib.check(lib.hawk_scan_gelu_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(gate_bias),
+                                          h.data_ptr(), yv.data_ptr(), yv.stride(0), yv.stride(1), dout.data_ptr(),
+                                          dx.data_ptr(), dgx.data_ptr(), dga.data_ptr(), dy_out.data_ptr(),
+                                          dy_out.stride(0), dy_out.stride(1), dlam.data_ptr(),
+                                          dgb.data_ptr() if gate_bias is not None else None, ws.data_ptr(), ws_bytes,
+                                          B, T, D, _dt(x), _stream(x)), "hawk_scan_gelu_bwd")
+    return dx, dgx, dga, dlam, dgb
+
+
+@scan_gelu_bwd_into.register_fake
+def _(x, gx, ga, lam, gate_bias, h, y, dout, dy_out):
+    D = x.shape[-1]
+    e = lambda: torch.empty_like(x, memory_format=torch.contiguous_format)
+    return (e(), e(), e(), x.new_empty(D, dtype=torch.float32),
+            x.new_empty(2 if gate_bias is not None else 0, D, dtype=torch.float32))
+
+
+class _ScanGelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gx, ga, lam, gate_bias, y):
+        h, out = scan_gelu_fwd(x, gx, ga, lam, gate_bias, y)
+        ctx.save_for_backward(x, gx, ga, lam, gate_bias, y, h)
+        ctx.mark_non_differentiable(h)
+        ctx.set_materialize_grads(False)
+        return out, h
+
+    @staticmethod
+    def backward(ctx, dout, _dh):
+        if dout is None:
+            return (None,) * 6
+        x, gx, ga, lam, gate_bias, y, h = ctx.saved_tensors
+        dy = torch.empty_like(x)
+        dx, dgx, dga, dlam, dgb = scan_gelu_bwd_into(x, gx, ga, lam, gate_bias, h, y, dout, dy)
+        return dx, dgx, dga, dlam, (dgb if gate_bias is not None else None), dy
+
+
+def fused_scan_gelu(x, x_rg_lru, a_rg_lru, a_param, y, *, gate_bias=None):
+    """(gelu(y) * h, h) with h = fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param): the RG-LRU scan and the
+    recurrent block's epilogue (hawk/hawk.py:134-135,186,201) in one kernel each way.  Dtype rules as
+    fused_linear_scan; h is returned for the decode cache and carries no gradient (use out)."""
+    dt = torch.bfloat16 if torch.is_autocast_enabled("cuda") else x.dtype
+    x, x_rg_lru, a_rg_lru, y = (t if t.dtype == dt else t.to(dt) for t in (x, x_rg_lru, a_rg_lru, y))
+    lam = a_param if a_param.dtype == torch.float32 else a_param.float()
+    if gate_bias is not None and gate_bias.dtype != torch.float32:
+        gate_bias = gate_bias.float()
+    return _ScanGelu.apply(x, x_rg_lru, a_rg_lru, lam, gate_bias, y)
+
+
+# ---------------------------------------------------------------------------------------------
+# temporal conv1d
+# ---------------------------------------------------------------------------------------------
 
 
 @torch.library.custom_op("hawk_b200::conv1d_fwd", mutates_args=())
@@ -860,7 +959,7 @@ def linear(x, w, w_bf16=None):
 # ---------------------------------------------------------------------------------------------
 class _RecurrentCore(torch.autograd.Function):
     """out = gelu(y) * scan(conv(x_b), gates(conv(x_b))) for xy = [x_b | y] (hawk/hawk.py:164-166,
-    181-199), and h.  The kernels are the ones the separate operators launch; what one node adds is the
+    181-199), and h.  The scan kernels carry the gelu(y) * h epilogue; what one node adds is the
     backward's bookkeeping: d y and d x_b are written straight into the two halves of d xy (no
     concatenation pass for the chunk), and the gate projections accumulate their input gradient onto
     the scan's (no separate add pass)."""
@@ -882,8 +981,7 @@ class _RecurrentCore(torch.autograd.Function):
             torch.bmm(xcb, wxc, out=gates[0].view(M, nb, bw).transpose(0, 1))
             torch.bmm(xcb, wac, out=gates[1].view(M, nb, bw).transpose(0, 1))
             gx, ga = gates[0].view(xc.shape), gates[1].view(xc.shape)
-            h = scan_fwd(xc, gx, ga, lam, None, gate_bias)
-            out = gelu_mul_fwd(y, h)
+            h, out = scan_gelu_fwd(xc, gx, ga, lam, gate_bias, y)  # scan and gelu(y) * h in one kernel
         ctx.save_for_backward(xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h)
         ctx.meta = (nb, bw, conv_w.dtype, conv_b.dtype, wx.dtype)
         ctx.mark_non_differentiable(h)
@@ -901,8 +999,7 @@ class _RecurrentCore(torch.autograd.Function):
         with torch.autocast("cuda", enabled=False):
             xb, y = xy[..., :R], xy[..., R:]
             dxy = torch.empty_like(xy)
-            dh = gelu_mul_bwd_into(dout.to(xy.dtype), y, h, dxy[..., R:])
-            dxc, dgx, dga, dlam, _, dgb = scan_bwd(xc, gx, ga, lam, None, gate_bias, h, dh)
+            dxc, dgx, dga, dlam, dgb = scan_gelu_bwd_into(xc, gx, ga, lam, gate_bias, h, y, dout, dxy[..., R:])
             gxb = dgx.view(M, nb, bw).transpose(0, 1)
             gab = dga.view(M, nb, bw).transpose(0, 1)
             xcT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define HAWK_B200_ABI_VERSION 2
+#define HAWK_B200_ABI_VERSION 3
 
 typedef enum hawk_dtype { HAWK_F32 = 0, HAWK_BF16 = 1 } hawk_dtype;
 
@@ -81,6 +81,25 @@ int hawk_scan_bwd(const void* x, const void* gx, const void* ga, const float* la
                   const float* gate_bias, const void* h, const void* go, void* dx, void* dgx, void* dga,
                   float* dlam, float* dh0, float* dgate_bias, void* workspace, size_t workspace_bytes,
                   int B, int T, int D, int dtype, void* stream);
+
+/* The scan with the recurrent block's epilogue fused in: out = gelu(y) * h (Hawk.epilogue,
+ * hawk/hawk.py:134-135, called at :201; exact erf GELU as torch.nn.functional.gelu).  Replaces the scan
+ * plus the separate pointwise pass over [B,T,D] that the reference runs after it, in both directions.
+ * y is the other half of the block's input projection (hawk/hawk.py:164-166), read in place: element
+ * (b,t,d) at y + b*y_batch_stride + t*y_row_stride + d (strides in ELEMENTS, multiples of 16 bytes, base
+ * 16-byte aligned).  Forward writes h (needed by the backward, and the decode state) and out, both
+ * [B,T,D] contiguous; out is formed from h as stored.  Backward takes dout = d loss / d out and writes
+ * dx, dgx, dga ([B,T,D] contiguous) and dy with its own strides (so it can land in the y half of the
+ * projection's gradient); h_t is recomputed from the stored h_{t-1}.  Initial state is zero.
+ * gate_bias / dgate_bias, lam / dlam and the workspace are as for hawk_scan_fwd / hawk_scan_bwd. */
+int hawk_scan_gelu_fwd(const void* x, const void* gx, const void* ga, const float* lam,
+                       const float* gate_bias, const void* y, int64_t y_batch_stride, int64_t y_row_stride,
+                       void* h, void* out, int B, int T, int D, int dtype, void* stream);
+int hawk_scan_gelu_bwd(const void* x, const void* gx, const void* ga, const float* lam,
+                       const float* gate_bias, const void* h, const void* y, int64_t y_batch_stride,
+                       int64_t y_row_stride, const void* dout, void* dx, void* dgx, void* dga, void* dy,
+                       int64_t dy_batch_stride, int64_t dy_row_stride, float* dlam, float* dgate_bias,
+                       void* workspace, size_t workspace_bytes, int B, int T, int D, int dtype, void* stream);
 
 /* hawk_scan_bwd for hosts that cannot allocate device memory (no counterpart in the reference, which
  * allocates its scratch with torch.empty on every call, hawk/scan_fused.py:378).  Same arguments and
