@@ -21,11 +21,10 @@
 //   warps 2-5: epilogue, tcgen05.ld 32 lanes x 32 columns at a time, overlapping the next tile's MMA.
 // Persistent over tiles (grid = min(tiles, SM count)).  Every mbarrier wait is bounded by a clock
 // budget; on expiry the kernel records a status word, drains, frees TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc05.cuh"
 
 namespace hawk {
+using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;  // one tcgen05.mma covers 128 x 256 x 16
 constexpr int A_HALF_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -42,7 +41,6 @@ struct GemmCfg {
   static constexpr int NACC = MH == 1 ? 2 : 1;
 };
 constexpr int GEMM_THREADS = 192;
-constexpr long long WAIT_BUDGET = 4000000000LL;  // clock cycles (~2 s) before a wait gives up
 
 enum { EPI_LOGITS = 0, EPI_F32 = 1 };
 
@@ -60,102 +58,8 @@ struct EpiParams {
   long long ldo;
 };
 
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the clock budget ran out (the caller abandons its loop).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_BUDGET) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzled rows
-// (rows of 64 bf16; 8-row groups 1024 bytes apart).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address
-  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: 8 rows x 128 B
-  d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
-  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-  return d;
-}
-
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = 256.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
+constexpr uint32_t kIdesc = umma_idesc(BM, BN);
 
 // tile index -> (m_tile, n_tile): groups of GROUP_M row tiles sweep all column tiles, so the tiles
 // in flight share a small set of A and B tiles in L2
@@ -199,12 +103,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(&tmem_base_slot, 512);
-  tc_fence_before();
+  fence_before();
   __syncthreads();
-  tc_fence_after();
+  fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
 
@@ -225,6 +129,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tma_load_2d(st + A_BYTES, &map_b, &full_bar[s], kb * BK, nt * BN);
         }
       }
+      // a wait gave up somewhere: let the copies issued last land before the CTA's shared memory goes
+      if (*abortp) drain_stages(full_bar, KSTAGES, it);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -234,22 +140,22 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int acc = NACC == 2 ? (tcount & 1) : 0;
         const uint32_t aph = NACC == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
         if (!mbar_wait(&tempty_bar[acc], aph ^ 1, abortp)) break;
-        tc_fence_after();
+        fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % KSTAGES;
           const uint32_t ph = (it / KSTAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abortp)) { ok = false; break; }
-          tc_fence_after();
+          fence_after();
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES_G);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
 #pragma unroll
             for (int hh = 0; hh < MH; ++hh) {  // the halves of a 256-row tile accumulate side by side in TMEM
-              umma_bf16(d_tmem + hh * BN, umma_desc(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 2),
-                        umma_desc(b_addr + k * UMMA_K * 2), (kb | k) ? 1u : 0u);
+              umma_bf16(d_tmem + hh * BN, umma_desc_sw128(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 2),
+                        umma_desc_sw128(b_addr + k * UMMA_K * 2), kIdesc, (kb | k) ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
@@ -268,8 +174,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tile_coords(tile, m_tiles, n_tiles, mt, nt);
       const int acc = NACC == 2 ? (tcount & 1) : 0;
       const uint32_t aph = NACC == 2 ? ((tcount >> 1) & 1) : (tcount & 1);
-      if (!mbar_wait(&tfull_bar[acc], aph, abortp)) break;
-      tc_fence_after();
+      if (!mbar_wait_warp(&tfull_bar[acc], aph, abortp)) break;  // lane 0 waits: the warp cannot diverge
+      fence_after();
       const int col0 = nt * BN;
 #pragma unroll 1
       for (int hh = 0; hh < MH; ++hh) {
@@ -343,7 +249,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
       }  // halves
-      tc_fence_before();
+      fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
@@ -351,18 +257,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   // ---------------- teardown ----------------
   __syncwarp();
-  tc_fence_before();
+  fence_before();
   __syncthreads();
-  if (abort_flag) {
-    if (threadIdx.x == 0) atomicExch(status, 1);
-    // let any bulk copy still in flight land before this CTA's shared memory is released
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-    __syncthreads();
-  }
+  if (abort_flag && threadIdx.x == 0) atomicExch(status, 1);
   if (warp == 1) {
-    tc_fence_after();
+    fence_after();
     tmem_dealloc(tmem_base, 512);
   }
 }
@@ -436,6 +335,12 @@ ce_loss_final_kernel(const float* __restrict__ partial, int n, float inv_n, floa
   if (threadIdx.x == 0) *loss = red[0] * inv_n;
 }
 
+// A GEMM of this call abandoned a wait: make that visible in the result itself (the loss becomes NaN),
+// since a training loop may not read the status word for many steps.
+__global__ void ce_poison_on_abort_kernel(const int* __restrict__ status, float* __restrict__ loss) {
+  if (*status != 0) *loss = __int_as_float(0x7fc00000);
+}
+
 // logits [N, ldl] bf16 -> dprobs = (exp(logit - lse) - onehot) / N, in place, and its transpose [V, ldt].
 // 64x64 tiles through shared memory; interior tiles move 16 bytes per thread in both directions.
 __global__ void __launch_bounds__(256)
@@ -506,49 +411,13 @@ ce_dprobs_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, __nv_bfloat1
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// 2-D bf16 tensor [rows, cols] with row pitch ld (elements); box = [box_rows, 64 cols], 128B swizzle
-static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int sm_count() {
-  int dev = 0, v = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-    v = 148;
-  return v;
-}
-
 // C[M, Nc] = A[M, K] . B[Nc, K]^T  (A, B bf16 row-major with pitches lda, ldb)
 template <int MH>
 static int launch_gemm(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* B, long long ldb, int M, int Nc, int K,
                        const EpiParams& ep, int* status, cudaStream_t st) {
   using Cfg = GemmCfg<MH>;
   CUtensorMap ma, mb;
-  if (!make_map(&ma, A, M, K, lda, BM * MH) || !make_map(&mb, B, Nc, K, ldb, BN)) return HAWK_ERR_DEVICE;
+  if (!make_map_bf16(&ma, A, M, K, lda, BM * MH) || !make_map_bf16(&mb, B, Nc, K, ldb, BN)) return HAWK_ERR_DEVICE;
   // per call: the attribute belongs to the current device's copy of the kernel
   if (cudaFuncSetAttribute(gemm_bf16_tn_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -623,7 +492,6 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
   auto* correct = reinterpret_cast<float*>(ws + L.correct);
   auto* lse = reinterpret_cast<float*>(ws + L.lse);
   auto* partial = reinterpret_cast<float*>(ws + L.partial);
-  (void)status;
 
   // 1. operands in bf16, both orientations
   {
@@ -638,7 +506,13 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     int rc = launch_status();
     if (rc != HAWK_OK) return rc;
   }
-  // 2. logits + online softmax statistics
+  // 2. logits + online softmax statistics.  The label's logit is written by the tile that holds the label;
+  // a label outside [0, V) matches no tile, so its slot keeps this NaN pattern and the loss comes out NaN
+  // (a label in the padding of the last tile picks -inf: the loss comes out +inf).
+  if (cudaMemsetAsync(correct, 0xFF, (size_t)N * sizeof(float), st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return HAWK_ERR_LAUNCH;
+  }
   {
     EpiParams ep{};
     ep.mode = EPI_LOGITS;
@@ -678,5 +552,6 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     rc = launch_gemm<2>(dpT, L.ldN, abT, L.ldN, (int)V, (int)H, (int)N, ep, status, st);
     if (rc != HAWK_OK) return rc;
   }
-  return HAWK_OK;
+  ce_poison_on_abort_kernel<<<1, 1, 0, st>>>(status, loss);
+  return launch_status();
 }

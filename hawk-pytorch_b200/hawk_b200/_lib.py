@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_longlong, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhawk_b200.so")
@@ -45,6 +45,12 @@ SIGNATURES = {
     "hawk_rms_norm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int, c_int, c_int, _P]),
     "hawk_add_rms_norm_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_float, c_int, c_int, _P]),
     "hawk_add_rms_norm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int, c_int, c_int, _P]),
+    "hawk_gates_packed_bytes": (c_size_t, [c_int, c_int]),
+    "hawk_gates_bwd_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
+    "hawk_gates_pack_weights": (c_int, [_P, _P, c_int, _P, c_int, c_int, _P]),
+    "hawk_gates_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_int, _P, _P]),
+    "hawk_gates_bwd": (c_int, [_P] * 8 + [c_size_t, c_int64, c_int, c_int, _P, _P]),
+    "hawk_debug_wait_timeout": (c_int, [_P, c_size_t, c_longlong, _P, _P]),
     "hawk_linear_ce_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "hawk_linear_ce_fwd_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_size_t, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }

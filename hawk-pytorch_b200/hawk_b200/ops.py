@@ -889,6 +889,114 @@ def block_diag_gates(x, wx, bx, wa, ba):
     return _BlockDiagGates.apply(x, wx, bx, wa, ba)
 
 
+# ---- the same two projections as one tcgen05 kernel per direction --------------------------------
+# bf16 bytes per [M, R] element: forward reads xc, writes gx, ga; backward reads xc, dgx, dga (the latter two
+# twice: input- and weight-gradient kernels) and reads + writes dxc
+GATE_BYTES_PER_ELEMENT = {"gates_fwd": 6, "gates_bwd": 14}
+
+
+def gates_kernel_ok(x: torch.Tensor, nb: int, bw: int) -> bool:
+    """Whether the fused gate kernels take this case: bf16 activations, block width dividing 128, width a
+    multiple of 128 (anything else runs the strided-batch cuBLAS form above)."""
+    R = nb * bw
+    return x.is_cuda and x.dtype == torch.bfloat16 and R % 128 == 0 and 8 <= bw <= 128 and 128 % bw == 0
+
+
+@torch.library.custom_op("hawk_b200::gates_pack", mutates_args=())
+def gates_pack(wx: torch.Tensor, wa: torch.Tensor) -> torch.Tensor:
+    """Both gate weights [nb, bw, bw] (fp32 or bf16) in the operand layouts of gates_fwd / gates_bwd (bf16)."""
+    lib = _lib.load()
+    nb, bw, _ = wx.shape
+    wx, wa = wx.contiguous(), wa.contiguous()
+    assert wa.shape == wx.shape and wa.dtype == wx.dtype
+    packed = torch.empty(lib.hawk_gates_packed_bytes(nb * bw, bw) // 2, dtype=torch.bfloat16, device=wx.device)
+    with _on(wx, "gates_pack", 1):
+        _lib.check(lib.hawk_gates_pack_weights(wx.data_ptr(), wa.data_ptr(), _dt(wx), packed.data_ptr(), nb * bw, bw,
+                                               _stream(wx)), "hawk_gates_pack_weights")
+    return packed
+
+
+@gates_pack.register_fake
+def _(wx, wa):
+    nb, bw, _ = wx.shape
+    return wx.new_empty(2 * (nb * bw // 128) * 256 * 128, dtype=torch.bfloat16)
+
+
+@torch.library.custom_op("hawk_b200::gates_fwd", mutates_args=())
+def gates_fwd(xc: torch.Tensor, packed: torch.Tensor, bw: int) -> torch.Tensor:
+    """[2, M, R]: (input-gate, recurrence-gate) projections of xc [M, R] bf16, without biases."""
+    lib = _lib.load()
+    xc = xc.contiguous()
+    M, R = xc.shape
+    out = torch.empty(2, M, R, dtype=xc.dtype, device=xc.device)
+    with _on(xc, "gates_fwd", 1):
+        _lib.check(lib.hawk_gates_fwd(xc.data_ptr(), packed.data_ptr(), out[0].data_ptr(), out[1].data_ptr(), M, R, bw,
+                                      _status_word(xc.device).data_ptr(), _stream(xc)), "hawk_gates_fwd")
+    return out
+
+
+@gates_fwd.register_fake
+def _(xc, packed, bw):
+    return xc.new_empty(2, xc.shape[0], xc.shape[1])
+
+
+@torch.library.custom_op("hawk_b200::gates_bwd_into", mutates_args=("dxc",))
+def gates_bwd_into(xc: torch.Tensor, dgx: torch.Tensor, dga: torch.Tensor, packed: torch.Tensor, dxc: torch.Tensor,
+                   bw: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """dxc += dgx Wx^T + dga Wa^T in place (dxc [M, R] bf16 contiguous); returns (dwx, dwa) [nb, bw, bw] fp32."""
+    lib = _lib.load()
+    xc, dgx, dga = xc.contiguous(), dgx.contiguous(), dga.contiguous()
+    M, R = xc.shape
+    assert dxc.is_contiguous() and dxc.shape == xc.shape and dxc.dtype == xc.dtype
+    nb = R // bw
+    dwx = torch.empty(nb, bw, bw, dtype=torch.float32, device=xc.device)
+    dwa = torch.empty(nb, bw, bw, dtype=torch.float32, device=xc.device)
+    ws_bytes = lib.hawk_gates_bwd_workspace_bytes(M, R, bw)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=xc.device)
+    with _on(xc, "gates_bwd", 3):
+        _lib.check(lib.hawk_gates_bwd(xc.data_ptr(), dgx.data_ptr(), dga.data_ptr(), packed.data_ptr(), dxc.data_ptr(),
+                                      dwx.data_ptr(), dwa.data_ptr(), ws.data_ptr(), ws_bytes, M, R, bw,
+                                      _status_word(xc.device).data_ptr(), _stream(xc)), "hawk_gates_bwd")
+    return dwx, dwa
+
+
+@gates_bwd_into.register_fake
+def _(xc, dgx, dga, packed, dxc, bw):
+    nb = xc.shape[1] // bw
+    return (xc.new_empty(nb, bw, bw, dtype=torch.float32), xc.new_empty(nb, bw, bw, dtype=torch.float32))
+
+
+class _FusedGates(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, wx, wa):
+        nb, bw, _ = wx.shape
+        x2 = x.reshape(-1, nb * bw)
+        packed = gates_pack(wx.detach(), wa.detach())
+        out = gates_fwd(x2, packed, bw)
+        ctx.save_for_backward(x2, packed)
+        ctx.meta = (x.shape, bw, wx.dtype)
+        return out[0].view(x.shape), out[1].view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dgx, dga):
+        x2, packed = ctx.saved_tensors
+        shape, bw, wdt = ctx.meta
+        dx = torch.zeros_like(x2)
+        dwx, dwa = gates_bwd_into(x2, dgx.reshape(x2.shape).to(x2.dtype), dga.reshape(x2.shape).to(x2.dtype), packed,
+                                  dx, bw)
+        return dx.view(shape), dwx.to(wdt), dwa.to(wdt)
+
+
+def fused_block_diag_gates(x, wx, wa):
+    """(input-gate, recurrence-gate) projections of x [..., R] WITHOUT biases by the fused kernels (see
+    gates_kernel_ok for the cases they take); differentiable in x, wx, wa."""
+    nb, bw, _ = wx.shape
+    if not gates_kernel_ok(x, nb, bw):
+        raise RuntimeError("hawk_b200: fused gate kernels need bf16 activations, block width dividing 128 and "
+                           "a width that is a multiple of 128")
+    return _FusedGates.apply(x, wx, wa)
+
+
 # ---------------------------------------------------------------------------------------------
 # bf16 projection of an fp32 parameter (what autocast makes of nn.Linear), with fewer passes
 # ---------------------------------------------------------------------------------------------
@@ -975,15 +1083,21 @@ class _RecurrentCore(torch.autograd.Function):
             dt = xy.dtype
             xc = conv1d_fwd(xb, conv_w, conv_b, dt)
             M = xc.numel() // R
-            gates = torch.empty(2, M, R, dtype=dt, device=xy.device)
-            wxc, wac = wx.to(dt), wa.to(dt)
-            xcb = xc.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
-            torch.bmm(xcb, wxc, out=gates[0].view(M, nb, bw).transpose(0, 1))
-            torch.bmm(xcb, wac, out=gates[1].view(M, nb, bw).transpose(0, 1))
+            fused = gates_kernel_ok(xc, nb, bw)
+            if fused:  # both projections in one tcgen05 kernel
+                wxc = gates_pack(wx.detach(), wa.detach())
+                wac = wxc
+                gates = gates_fwd(xc.view(M, R), wxc, bw)
+            else:      # strided-batch cuBLAS GEMMs on the final layout
+                gates = torch.empty(2, M, R, dtype=dt, device=xy.device)
+                wxc, wac = wx.to(dt), wa.to(dt)
+                xcb = xc.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
+                torch.bmm(xcb, wxc, out=gates[0].view(M, nb, bw).transpose(0, 1))
+                torch.bmm(xcb, wac, out=gates[1].view(M, nb, bw).transpose(0, 1))
             gx, ga = gates[0].view(xc.shape), gates[1].view(xc.shape)
             h, out = scan_gelu_fwd(xc, gx, ga, lam, gate_bias, y)  # scan and gelu(y) * h in one kernel
         ctx.save_for_backward(xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h)
-        ctx.meta = (nb, bw, conv_w.dtype, conv_b.dtype, wx.dtype)
+        ctx.meta = (nb, bw, conv_w.dtype, conv_b.dtype, wx.dtype, fused)
         ctx.mark_non_differentiable(h)
         ctx.set_materialize_grads(False)  # no zero-filled [B,T,R] gradient for h on every backward
         return out, h
@@ -993,21 +1107,24 @@ class _RecurrentCore(torch.autograd.Function):
         if dout is None:
             return (None,) * 7
         xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h = ctx.saved_tensors
-        nb, bw, cwdt, cbdt, wdt = ctx.meta
+        nb, bw, cwdt, cbdt, wdt, fused = ctx.meta
         R = xy.shape[-1] // 2
         M = xc.numel() // R
         with torch.autocast("cuda", enabled=False):
             xb, y = xy[..., :R], xy[..., R:]
             dxy = torch.empty_like(xy)
             dxc, dgx, dga, dlam, dgb = scan_gelu_bwd_into(xc, gx, ga, lam, gate_bias, h, y, dout, dxy[..., R:])
-            gxb = dgx.view(M, nb, bw).transpose(0, 1)
-            gab = dga.view(M, nb, bw).transpose(0, 1)
-            xcT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
-            dwx = torch.bmm(xcT, gxb)
-            dwa = torch.bmm(xcT, gab)
-            dxcb = dxc.view(M, nb, bw).transpose(0, 1)
-            torch.baddbmm(dxcb, gxb, wxc.transpose(1, 2), out=dxcb)  # d xc (scan) += d gx Wx^T + d ga Wa^T
-            torch.baddbmm(dxcb, gab, wac.transpose(1, 2), out=dxcb)
+            if fused:  # d xc (scan) += d gx Wx^T + d ga Wa^T in place, and both weight gradients
+                dwx, dwa = gates_bwd_into(xc.view(M, R), dgx.view(M, R), dga.view(M, R), wxc, dxc.view(M, R), bw)
+            else:
+                gxb = dgx.view(M, nb, bw).transpose(0, 1)
+                gab = dga.view(M, nb, bw).transpose(0, 1)
+                xcT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
+                dwx = torch.bmm(xcT, gxb)
+                dwa = torch.bmm(xcT, gab)
+                dxcb = dxc.view(M, nb, bw).transpose(0, 1)
+                torch.baddbmm(dxcb, gxb, wxc.transpose(1, 2), out=dxcb)
+                torch.baddbmm(dxcb, gab, wac.transpose(1, 2), out=dxcb)
             dcw, dcb = conv1d_bwd_into(dxc, xb, conv_w, dxy[..., :R])
         return dxy, dcw.to(cwdt), dcb.to(cbdt), dwx.to(wdt), dwa.to(wdt), dgb, dlam
 

@@ -172,12 +172,51 @@ int hawk_decode_block_step(const void* xy, int64_t xy_row_stride, void* conv_sta
  * H must be a multiple of 8.  Workspace: hawk_linear_ce_workspace_bytes(N, H, V), 256-byte aligned
  * (bf16 operand copies, the [N,V] bf16 logits/dprobs buffer and its transpose, row statistics).
  * status: one int32 in device memory, zeroed by the caller once; a kernel whose bounded wait on an
- * mbarrier ran out sets it to 1 (the results of that call are then invalid) instead of hanging.
+ * mbarrier ran out sets it to 1 (the results of that call are then invalid) instead of hanging, and the
+ * call then also overwrites `loss` with NaN, so a caller that never reads the status word still sees it.
+ * Labels must lie in [0, V) (the reference's gather would raise otherwise, fused_cross_entropy.py:37-39;
+ * it has no ignore_index): a label outside the range makes `loss` non-finite (NaN or inf).
  * ---------------------------------------------------------------------------------------- */
 size_t hawk_linear_ce_workspace_bytes(int64_t N, int64_t H, int64_t V);
 int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const int64_t* labels, float* loss,
                            float* dweight, float* dact, void* workspace, size_t workspace_bytes,
                            int64_t N, int64_t H, int64_t V, int dtype, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Both block-diagonal gate projections of the recurrent block, one pass per direction.  Replaces the two
+ * BlockDiagonalLinear.forward calls (hawk/external.py:224-233, called at hawk/hawk.py:181-182: einsum ->
+ * two bmm launches that each re-read the conv output) and the four GEMMs of their backward.  The biases
+ * (external.py:230) are not added here: pass them to the scan as gate_bias.
+ *
+ *   forward : gx[m, n*bw + j] = sum_i xc[m, n*bw + i] * wx[n][i][j]   (ga likewise with wa)
+ *   backward: dxc[m, n*bw + i] += sum_j dgx[m, n*bw + j] * wx[n][i][j] + dga[..] * wa[n][i][j]  (IN PLACE: dxc
+ *             arrives holding the scan's input gradient), dwx[n][i][j] = sum_m xc[m, n*bw+i] * dgx[m, n*bw+j]
+ *             (dwa likewise), summed in a fixed order.
+ *
+ * xc, gx, ga, dgx, dga, dxc: [M, R] contiguous bf16 (M = batch * time); wx, wa: [R/bw, bw, bw] in `w_dtype`;
+ * dwx, dwa: the same shape in fp32.  bw must divide 128 (>= 8) and R be a multiple of 128.  tcgen05 GEMMs
+ * with bf16 operands and fp32 accumulation: the arithmetic of the reference's einsum under autocast.
+ * hawk_gates_pack_weights converts both weights once per step into the operand layouts of the kernels
+ * (`packed`, hawk_gates_packed_bytes(R, bw) bytes, 16-byte aligned), used by forward and backward.
+ * Backward workspace: hawk_gates_bwd_workspace_bytes(M, R, bw), 16-byte aligned.  status: as for
+ * hawk_linear_ce_fwd_bwd.
+ * ---------------------------------------------------------------------------------------- */
+size_t hawk_gates_packed_bytes(int R, int bw);
+size_t hawk_gates_bwd_workspace_bytes(int64_t M, int R, int bw);
+int hawk_gates_pack_weights(const void* wx, const void* wa, int w_dtype, void* packed, int R, int bw,
+                            void* stream);
+int hawk_gates_fwd(const void* xc, const void* packed, void* gx, void* ga, int64_t M, int R, int bw,
+                   int* status, void* stream);
+int hawk_gates_bwd(const void* xc, const void* dgx, const void* dga, const void* packed, void* dxc, float* dwx,
+                   float* dwa, void* workspace, size_t workspace_bytes, int64_t M, int R, int bw, int* status,
+                   void* stream);
+
+/* Shows that a device-side wait of the tcgen05 kernels gives up instead of hanging (no counterpart in
+ * the reference): launches one 128 x 128 tile of the gate-projection kernel inside `scratch` (>= 229376
+ * bytes, 256-byte aligned) with its TMA producer switched off and a wait budget of `budget_cycles` clock
+ * cycles (1e3 .. 1e8).  The kernel must return by itself and set *status to 1. */
+int hawk_debug_wait_timeout(void* scratch, size_t scratch_bytes, long long budget_cycles, int* status,
+                            void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Glue of the block around the GEMMs, one HBM pass each (reference: eager torch ops).

@@ -105,3 +105,19 @@ def test_linear_ce_config2_shape_properties():
     da_ref = ((torch.softmax(logits, -1) - torch.nn.functional.one_hot(labels[idx], V)) @ w.double()) / N
     assert rel_l2(da[idx].cpu(), da_ref.cpu()) <= TOL
     assert float(ref_rows.mean()) > 0
+
+
+def test_label_outside_the_vocabulary_is_visible_in_the_loss():
+    """The reference's gather raises on a label outside [0, V) (hawk/fused_cross_entropy.py:37-39; it has no
+    ignore_index).  The kernel cannot raise: such a label makes the loss non-finite instead of silently wrong."""
+    from hawk_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    w = (torch.randn(300, 64, generator=g) / 8).cuda()
+    act = torch.randn(200, 64, generator=g).cuda()
+    labels = torch.randint(0, 300, (200,), generator=g).cuda()
+    assert bool(torch.isfinite(ops.fused_cross_entropy(w, act, labels)))
+    labels[17] = -100
+    assert not bool(torch.isfinite(ops.fused_cross_entropy(w, act, labels)))
+    labels[17] = 300
+    assert not bool(torch.isfinite(ops.fused_cross_entropy(w, act, labels)))
+    ops.check_device_status()
