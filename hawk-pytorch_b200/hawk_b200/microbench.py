@@ -1,6 +1,8 @@
 """Times one operator of this library in isolation (CUDA events, median of N launches).
 
     python -m hawk_b200.microbench scan      [--B 8 --T 4096 --D 2048 --dtype bf16]
+    python -m hawk_b200.microbench scan_gelu [--B 8 --T 4096 --D 2048 --dtype bf16]   # scan with gelu(y)*h fused in
+    python -m hawk_b200.microbench gates     [--B 8 --T 4096 --D 2048 --bw 128]       # both gate projections
     python -m hawk_b200.microbench conv1d    [--B 8 --T 4096 --D 2048 --dtype bf16]
     python -m hawk_b200.microbench linear_ce [--N 32760 --H 2048 --V 32000]
     python -m hawk_b200.microbench glue      [--N 32768 --H 2048 --J 6144]   # gelu(a)*b and add+RMSNorm, both ways
@@ -8,7 +10,8 @@
     python -m hawk_b200.microbench decode_model [--B 256]   # one cached token of the 1.35 B model, eager vs CUDA graph
 
 Prints one JSON line per kernel with the achieved rate against its algorithmic work:
-scan 8 (forward) / 16 (backward) bytes per element in bf16, conv1d 4 / 6, linear_ce 6*N*H*V flop,
+scan 8 (forward) / 16 (backward) bytes per element in bf16 (12 / 20 with the fused gelu(y)*h epilogue), gate
+projections 6 / 14, conv1d 4 / 6, linear_ce 6*N*H*V flop,
 decode 8*B*D*elem bytes per step; glue: the tensors each kernel must read and write once (gelu(a)*b:
 3 / 5 bf16 tensors of N x J; add+RMSNorm with an fp32 residual stream and bf16 branch: 12 / 16 bytes per
 element).  Inputs are seeded normal draws; Lambda sits on the reference's
@@ -55,7 +58,8 @@ def _emit(name, ms, work, unit, **extra):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["scan", "conv1d", "linear_ce", "glue", "decode", "decode_model"])
+    ap.add_argument("op", choices=["scan", "scan_gelu", "gates", "conv1d", "linear_ce", "glue", "decode", "decode_model"])
+    ap.add_argument("--bw", type=int, default=128)
     ap.add_argument("--J", type=int, default=6144)
     ap.add_argument("--B", type=int, default=None)
     ap.add_argument("--T", type=int, default=4096)
@@ -89,6 +93,48 @@ def main(argv=None):
         _emit("scan_fwd", tf, 4 * es * n, "GB/s", **shape)
         _emit("scan_bwd", tb, 8 * es * n, "GB/s", **shape)
         _emit("scan_fwd+bwd", tf + tb, 12 * es * n, "GB/s", **shape)
+    elif a.op == "scan_gelu":
+        x, gx, ga, go = (torch.randn(a.B, a.T, a.D, generator=g, device=dev).to(dt) for _ in range(4))
+        xy = torch.randn(a.B, a.T, 2 * a.D, generator=g, device=dev).to(dt)
+        y = xy[..., a.D:]  # the strided half the model passes
+        dxy = torch.empty_like(xy)
+        lam = ring_init_(torch.empty(a.D)).to(dev)
+        n = a.B * a.T * a.D
+        gb = 0.1 * torch.randn(2, a.D, generator=g, device=dev)
+        h, _ = ops.scan_gelu_fwd(x, gx, ga, lam, gb, y)
+        tf = _time(lambda: ops.scan_gelu_fwd(x, gx, ga, lam, gb, y), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.scan_gelu_bwd_into(x, gx, ga, lam, gb, h, y, go, dxy[..., a.D:]), a.iters, a.warmup, flush)
+        _emit("scan_gelu_fwd", tf, 6 * es * n, "GB/s", **shape)
+        _emit("scan_gelu_bwd", tb, 10 * es * n, "GB/s", **shape)
+        _emit("scan_gelu_fwd+bwd", tf + tb, 16 * es * n, "GB/s", **shape)
+    elif a.op == "gates":
+        M, R, bw = a.B * a.T, a.D, a.bw
+        nb = R // bw
+        xc, dgx, dga, dxc = (torch.randn(M, R, generator=g, device=dev).bfloat16() for _ in range(4))
+        wx, wa = (torch.randn(nb, bw, bw, generator=g, device=dev) / math.sqrt(bw) for _ in range(2))
+        packed = ops.gates_pack(wx, wa)
+        tf = _time(lambda: ops.gates_fwd(xc, packed, bw), a.iters, a.warmup, flush)
+        tb = _time(lambda: ops.gates_bwd_into(xc, dgx, dga, packed, dxc, bw), a.iters, a.warmup, flush)
+        ops.check_device_status()
+        _emit("gates_fwd", tf, 6 * M * R, "GB/s", M=M, R=R, bw=bw)
+        _emit("gates_bwd", tb, 14 * M * R, "GB/s", M=M, R=R, bw=bw)
+        # the strided-batch cuBLAS form of the same work
+        def bmm_fwd():
+            xb = xc.view(M, nb, bw).transpose(0, 1)
+            out = torch.empty(2, M, R, dtype=torch.bfloat16, device=dev)
+            torch.bmm(xb, wxb, out=out[0].view(M, nb, bw).transpose(0, 1))
+            torch.bmm(xb, wab, out=out[1].view(M, nb, bw).transpose(0, 1))
+        def bmm_bwd():
+            gxb, gab = dgx.view(M, nb, bw).transpose(0, 1), dga.view(M, nb, bw).transpose(0, 1)
+            xT = xc.view(M, nb, bw).permute(1, 2, 0)
+            torch.bmm(xT, gxb)
+            torch.bmm(xT, gab)
+            d = dxc.view(M, nb, bw).transpose(0, 1)
+            torch.baddbmm(d, gxb, wxb.transpose(1, 2), out=d)
+            torch.baddbmm(d, gab, wab.transpose(1, 2), out=d)
+        wxb, wab = wx.bfloat16(), wa.bfloat16()
+        _emit("gates_fwd_cublas_bmm", _time(bmm_fwd, a.iters, a.warmup, flush), 6 * M * R, "GB/s", M=M, R=R, bw=bw)
+        _emit("gates_bwd_cublas_bmm", _time(bmm_bwd, a.iters, a.warmup, flush), 14 * M * R, "GB/s", M=M, R=R, bw=bw)
     elif a.op == "conv1d":
         xy = torch.randn(a.B, a.T, 2 * a.D, generator=g, device=dev).to(dt)
         xv = xy[..., :a.D]  # the strided half the model passes
