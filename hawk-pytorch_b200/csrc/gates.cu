@@ -20,7 +20,8 @@
 //
 // Operand layouts (packed by gates_pack_kernel, bf16):
 //   W2T [nsb][256][128] : row g*128 + j, column i  = W_g[blk][i][j]   B operand of the forward (K = i)
-//   W2  [nsb][128][256] : row i, column g*128 + j  = W_g[blk][i][j]   B operand of d input (K = (g, j))
+//   W2I [nsb][128][384] : row i, column g*128 + j  = W_g[blk][i][j]   B operand of d input (K = (g, j)),
+//                         columns 256..383 = identity (the scan's gradient passes through the GEMM)
 // The d-weight GEMM contracts over the M rows, which are the slow index of every activation tensor: its
 // operands are read as MN-major tiles (rows = K), so no transposed copy of xc / dgx / dga is ever made.
 #include "tc05.cuh"
@@ -32,15 +33,19 @@ constexpr int G_THREADS = 192;
 constexpr int SBW = 128;                  // super-block width
 constexpr int BOX128 = 128 * 128;         // bytes of a [64 x 128-row] box
 constexpr int BOX64 = 64 * 128;           // bytes of a [64 x 64-row] box
-constexpr int FWD_STAGES = 4, FWD_STAGE_BYTES = 2 * BOX128, FWD_W_BYTES = 2 * 256 * 128;
-constexpr int DX_STAGES = 2, DX_STAGE_BYTES = 4 * BOX128, DX_W_BYTES = 4 * BOX128;
+// forward: resident W2T (64 KB) | ring of xc tiles (2 boxes each) | staged [gx | ga] tile for the TMA store
+constexpr int FWD_STAGES = 2, FWD_STAGE_BYTES = 2 * BOX128, FWD_W_BYTES = 2 * 256 * 128, FWD_OUT_BYTES = 4 * BOX128;
+// d input: resident [W2 | I] (6 boxes) | ring of single boxes (dgx, dgx, dga, dga, dxc, dxc per tile) | staged dxc tile
+constexpr int DX_KB = 6, DX_STAGES = 6, DX_STAGE_BYTES = BOX128, DX_W_BYTES = DX_KB * BOX128, DX_OUT_BYTES = 2 * BOX128;
 constexpr int DW_STAGES = 4, DW_STAGE_BYTES = 6 * BOX64;
-constexpr int FWD_SMEM = FWD_W_BYTES + FWD_STAGES * FWD_STAGE_BYTES + 1024;
-constexpr int DX_SMEM = DX_W_BYTES + DX_STAGES * DX_STAGE_BYTES + 1024;
+constexpr int FWD_SMEM = FWD_W_BYTES + FWD_STAGES * FWD_STAGE_BYTES + FWD_OUT_BYTES + 1024;
+constexpr int DX_SMEM = DX_W_BYTES + DX_STAGES * DX_STAGE_BYTES + DX_OUT_BYTES + 1024;
 constexpr int DW_SMEM = DW_STAGES * DW_STAGE_BYTES + 1024;
+constexpr int MAX_STAGES = 6;
+constexpr int EPI_THREADS = 128, EPI_BARRIER = 1, EPI_LEADER = 64;  // warps 2-5; thread 64 issues the TMA stores
 
 struct GateBars {  // barrier block shared by the three kernels (not all are used by each)
-  uint64_t wfull, full[4], empty[4], tfull[2], tempty[2];
+  uint64_t wfull, full[MAX_STAGES], empty[MAX_STAGES], tfull[2], tempty[2];
 };
 
 __device__ __forceinline__ unsigned char* align1024(unsigned char* p) {
@@ -51,7 +56,7 @@ __device__ __forceinline__ void gate_setup(GateBars& b, uint32_t* tmem_slot, int
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(&b.wfull, 1);
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&b.full[s], 1);
       mbar_init(&b.empty[s], 1);
     }
@@ -78,20 +83,38 @@ __device__ __forceinline__ void gate_teardown(int* abort_flag, int* status, int 
   }
 }
 
+// Epilogue staging: TMEM lane `row` (0..127), 32 fp32 columns starting at column 32*c of the accumulator,
+// rounded to bf16 and written into the staged output tile in the layout a TMA store of [64-column x
+// 128-row] boxes with 128-byte swizzle expects (box c/2, 16-byte piece index XOR row mod 8: conflict-free).
+__device__ __forceinline__ void stage_chunk_bf16(unsigned char* out, int row, int c, const uint32_t (&v)[32]) {
+  unsigned char* base = out + (c >> 1) * BOX128 + row * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 o;
+    o.x = pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
+    o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+    o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+    o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+    const int piece = ((c & 1) * 4 + q) ^ (row & 7);
+    *reinterpret_cast<uint4*>(base + piece * 16) = o;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // forward: [gx | ga] tile (128 x 256) = xc tile (128 x 128) . W2T[sb]^T
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(G_THREADS, 1)
 gates_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 __nv_bfloat16* __restrict__ gx, __nv_bfloat16* __restrict__ ga, int M, int R, int nsb, int m_tiles,
-                 long long wait_budget, int producer_off, int* status) {
+                 const __grid_constant__ CUtensorMap map_gx, const __grid_constant__ CUtensorMap map_ga, int nsb,
+                 int m_tiles, long long wait_budget, int producer_off, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = align1024(smem_raw);
   unsigned char* wsm = smem;
   unsigned char* ring = smem + FWD_W_BYTES;
+  unsigned char* outsm = ring + FWD_STAGES * FWD_STAGE_BYTES;
   __shared__ __align__(8) GateBars bars;
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, epi_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   gate_setup(bars, &tmem_slot, &abort_flag, warp, 512);
   const uint32_t tmem_base = tmem_slot;
@@ -137,53 +160,65 @@ gates_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
     }
   } else {
+    // The tile is rounded to bf16 into shared memory and leaves as four TMA box stores (full lines, rows past
+    // M clipped by the unit); the staging buffer is reused once the previous tile's stores have read it.
     const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     uint32_t it = 0;
     for (int tile = tile0; tile < m_tiles; tile += tstride, ++it) {
       const int acc = it & 1;
-      if (!mbar_wait_warp(&bars.tfull[acc], (it >> 1) & 1, abortp, wait_budget)) break;
+      // one thread waits for the accumulator (and for the previous stores to have read the staging buffer);
+      // the four warps take its verdict together, so none can be left behind at a barrier
+      if (threadIdx.x == EPI_LEADER) {
+        epi_ok = mbar_wait(&bars.tfull[acc], (it >> 1) & 1, abortp, wait_budget) ? 1 : 0;
+        bulk_wait_read();
+      }
+      named_barrier(EPI_BARRIER, EPI_THREADS);
+      if (!epi_ok) break;
       fence_after();
-      const long long row = (long long)tile * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t v[32];
         tmem_ld32(taddr + c * 32, v);
-        if (row < M) {
-          __nv_bfloat16* dst = (c < 4 ? gx : ga) + row * R + sb * SBW + (c & 3) * 32;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
-            o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-            o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-            o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-            *reinterpret_cast<uint4*>(dst + q * 8) = o;
-          }
-        }
+        stage_chunk_bf16(outsm, row, c, v);
       }
       fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars.tempty[acc]);
+      if (lane == 0) mbar_arrive(&bars.tempty[acc]);  // the accumulator is free for the tile after next
+      fence_smem_to_tma();
+      named_barrier(EPI_BARRIER, EPI_THREADS);
+      if (threadIdx.x == EPI_LEADER) {
+        tma_store_2d(&map_gx, outsm, sb * SBW, tile * 128);
+        tma_store_2d(&map_gx, outsm + BOX128, sb * SBW + 64, tile * 128);
+        tma_store_2d(&map_ga, outsm + 2 * BOX128, sb * SBW, tile * 128);
+        tma_store_2d(&map_ga, outsm + 3 * BOX128, sb * SBW + 64, tile * 128);
+        bulk_commit();
+      }
     }
+    if (threadIdx.x == EPI_LEADER) bulk_wait_all();
   }
   gate_teardown(&abort_flag, status, warp, tmem_base, 512);
 }
 
 // ---------------------------------------------------------------------------------------------
-// d input: dxc tile (128 x 128) += [dgx | dga] tile (128 x 256) . W2[sb]^T
+// d input: dxc tile (128 x 128) = [dgx | dga | dxc] tile (128 x 384) . [W2[sb] | I]^T
+// The scan's input gradient already in dxc rides through the GEMM as a third K segment against an identity
+// block, so the accumulate costs no epilogue reads: the tile is loaded by TMA like the other operands and the
+// result overwrites it by TMA store.  One ring stage = one [64 x 128-row] box (6 per tile).
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(G_THREADS, 1)
 gates_dx_kernel(const __grid_constant__ CUtensorMap map_dgx, const __grid_constant__ CUtensorMap map_dga,
-                const __grid_constant__ CUtensorMap map_w, __nv_bfloat16* __restrict__ dxc, int M, int R, int nsb,
+                const __grid_constant__ CUtensorMap map_dxc, const __grid_constant__ CUtensorMap map_w, int nsb,
                 int m_tiles, int* status) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = align1024(smem_raw);
   unsigned char* wsm = smem;
   unsigned char* ring = smem + DX_W_BYTES;
+  unsigned char* outsm = ring + DX_STAGES * DX_STAGE_BYTES;
   __shared__ __align__(8) GateBars bars;
   __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, epi_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   gate_setup(bars, &tmem_slot, &abort_flag, warp, 256);
   const uint32_t tmem_base = tmem_slot;
@@ -194,74 +229,76 @@ gates_dx_kernel(const __grid_constant__ CUtensorMap map_dgx, const __grid_consta
   if (warp == 0) {
     if (lane == 0) {
       mbar_arrive_expect_tx(&bars.wfull, DX_W_BYTES);
-      for (int kb = 0; kb < 4; ++kb) tma_load_2d(wsm + kb * BOX128, &map_w, &bars.wfull, kb * 64, sb * 128);
+      for (int kb = 0; kb < DX_KB; ++kb) tma_load_2d(wsm + kb * BOX128, &map_w, &bars.wfull, kb * 64, sb * 128);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = tile0; tile < m_tiles; tile += tstride, ++it) {
-        const int s = it % DX_STAGES;
-        if (!mbar_wait(&bars.empty[s], ((it / DX_STAGES) & 1) ^ 1, abortp)) { ok = false; break; }
-        mbar_arrive_expect_tx(&bars.full[s], DX_STAGE_BYTES);
-        unsigned char* st = ring + s * DX_STAGE_BYTES;
-        tma_load_2d(st, &map_dgx, &bars.full[s], sb * SBW, tile * 128);
-        tma_load_2d(st + BOX128, &map_dgx, &bars.full[s], sb * SBW + 64, tile * 128);
-        tma_load_2d(st + 2 * BOX128, &map_dga, &bars.full[s], sb * SBW, tile * 128);
-        tma_load_2d(st + 3 * BOX128, &map_dga, &bars.full[s], sb * SBW + 64, tile * 128);
+      for (int tile = tile0; ok && tile < m_tiles; tile += tstride) {
+        for (int kb = 0; kb < DX_KB; ++kb, ++it) {
+          const int s = it % DX_STAGES;
+          if (!mbar_wait(&bars.empty[s], ((it / DX_STAGES) & 1) ^ 1, abortp)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars.full[s], DX_STAGE_BYTES);
+          const CUtensorMap* src = kb < 2 ? &map_dgx : (kb < 4 ? &map_dga : &map_dxc);
+          tma_load_2d(ring + s * DX_STAGE_BYTES, src, &bars.full[s], sb * SBW + (kb & 1) * 64, tile * 128);
+        }
       }
       if (!ok || *abortp) drain_stages(bars.full, DX_STAGES, it);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = mbar_wait(&bars.wfull, 0, abortp);
-      uint32_t it = 0;
-      for (int tile = tile0; ok && tile < m_tiles; tile += tstride, ++it) {
-        const int acc = it & 1, s = it % DX_STAGES;
-        if (!mbar_wait(&bars.tempty[acc], ((it >> 1) & 1) ^ 1, abortp)) break;
-        if (!mbar_wait(&bars.full[s], (it / DX_STAGES) & 1, abortp)) break;
+      uint32_t it = 0, tcount = 0;
+      for (int tile = tile0; ok && tile < m_tiles; tile += tstride, ++tcount) {
+        const int acc = tcount & 1;
+        if (!mbar_wait(&bars.tempty[acc], ((tcount >> 1) & 1) ^ 1, abortp)) break;
         fence_after();
-        const uint32_t a_addr = smem_u32(ring + s * DX_STAGE_BYTES), b_addr = smem_u32(wsm);
-#pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
+        for (int kb = 0; kb < DX_KB; ++kb, ++it) {
+          const int s = it % DX_STAGES;
+          if (!mbar_wait(&bars.full[s], (it / DX_STAGES) & 1, abortp)) { ok = false; break; }
+          fence_after();
+          const uint32_t a_addr = smem_u32(ring + s * DX_STAGE_BYTES), b_addr = smem_u32(wsm + kb * BOX128);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + acc * 128, umma_desc_sw128(a_addr + kb * BOX128 + k * 32),
-                      umma_desc_sw128(b_addr + kb * BOX128 + k * 32), kIdesc, (kb | k) ? 1u : 0u);
-        umma_commit(&bars.empty[s]);
-        umma_commit(&bars.tfull[acc]);
+            umma_bf16(tmem_base + acc * 128, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), kIdesc,
+                      (kb | k) ? 1u : 0u);
+          umma_commit(&bars.empty[s]);
+        }
+        if (ok) umma_commit(&bars.tfull[acc]);
       }
     }
   } else {
     const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
     uint32_t it = 0;
     for (int tile = tile0; tile < m_tiles; tile += tstride, ++it) {
       const int acc = it & 1;
-      if (!mbar_wait_warp(&bars.tfull[acc], (it >> 1) & 1, abortp)) break;
+      // one thread waits for the accumulator (and for the previous stores to have read the staging buffer);
+      // the four warps take its verdict together, so none can be left behind at a barrier
+      if (threadIdx.x == EPI_LEADER) {
+        epi_ok = mbar_wait(&bars.tfull[acc], (it >> 1) & 1, abortp) ? 1 : 0;
+        bulk_wait_read();
+      }
+      named_barrier(EPI_BARRIER, EPI_THREADS);
+      if (!epi_ok) break;
       fence_after();
-      const long long row = (long long)tile * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 128);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld32(taddr + c * 32, v);
-        if (row < M) {
-          __nv_bfloat16* dst = dxc + row * R + sb * SBW + c * 32;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 in = *reinterpret_cast<const uint4*>(dst + q * 8);
-            const uint32_t iw[4] = {in.x, in.y, in.z, in.w};
-            uint32_t ow[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = unpack_bf16x2(iw[e]);
-              ow[e] = pack_bf16x2(f.x + __uint_as_float(v[8 * q + 2 * e]), f.y + __uint_as_float(v[8 * q + 2 * e + 1]));
-            }
-            *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-          }
-        }
+        stage_chunk_bf16(outsm, row, c, v);
       }
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.tempty[acc]);
+      fence_smem_to_tma();
+      named_barrier(EPI_BARRIER, EPI_THREADS);
+      if (threadIdx.x == EPI_LEADER) {
+        tma_store_2d(&map_dxc, outsm, sb * SBW, tile * 128);
+        tma_store_2d(&map_dxc, outsm + BOX128, sb * SBW + 64, tile * 128);
+        bulk_commit();
+      }
     }
+    if (threadIdx.x == EPI_LEADER) bulk_wait_all();
   }
   gate_teardown(&abort_flag, status, warp, tmem_base, 256);
 }
@@ -368,7 +405,7 @@ gates_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw
   (g ? dwa : dwx)[((size_t)blk * bw + i) * bw + j] = s;
 }
 
-// packed[0] = W2T [nsb][256][128], packed[1] = W2 [nsb][128][256] (see the head of this file)
+// packed[0] = W2T [nsb][256][128], then W2I [nsb][128][384] = [W2 | I] (see the head of this file)
 template <typename TW>
 __global__ void __launch_bounds__(256)
 gates_pack_kernel(const TW* __restrict__ wx, const TW* __restrict__ wa, __nv_bfloat16* __restrict__ packed, int nsb, int bw) {
@@ -387,7 +424,9 @@ gates_pack_kernel(const TW* __restrict__ wx, const TW* __restrict__ wa, __nv_bfl
   }
   const __nv_bfloat16 b = __float2bfloat16(v);
   packed[idx] = b;                                                        // W2T[sb][go][ci]
-  packed[n + ((size_t)sb * 128 + ci) * 256 + go] = b;                     // W2[sb][ci][go]
+  __nv_bfloat16* w2i = packed + n + ((size_t)sb * 128 + ci) * 384;
+  w2i[go] = b;                                                            // W2I[sb][ci][go]
+  if (g == 0) w2i[256 + co] = __float2bfloat16(ci == co ? 1.f : 0.f);     // the identity segment
 }
 
 static bool gates_shape_ok(int64_t M, int R, int bw) {
@@ -406,7 +445,7 @@ using namespace hawk;
 
 extern "C" size_t hawk_gates_packed_bytes(int R, int bw) {
   if (!gates_shape_ok(1, R, bw)) return 0;
-  return 2 * (size_t)(R / SBW) * 256 * 128 * sizeof(__nv_bfloat16);
+  return (size_t)(R / SBW) * (256 * 128 + 128 * 384) * sizeof(__nv_bfloat16);
 }
 
 extern "C" size_t hawk_gates_bwd_workspace_bytes(int64_t M, int R, int bw) {
@@ -438,17 +477,17 @@ static int gates_fwd_launch(const void* xc, const void* packed, void* gx, void* 
                             long long wait_budget, int producer_off, int* status, cudaStream_t st) {
   const int nsb = R / SBW;
   const int m_tiles = (int)((M + 127) / 128);
-  CUtensorMap mx, mw;
-  if (!make_map_bf16(&mx, xc, M, R, R, 128) || !make_map_bf16(&mw, packed, (long long)nsb * 256, 128, 128, 256))
+  CUtensorMap mx, mw, mgx, mga;
+  if (!make_map_bf16(&mx, xc, M, R, R, 128) || !make_map_bf16(&mw, packed, (long long)nsb * 256, 128, 128, 256) ||
+      !make_map_bf16(&mgx, gx, M, R, R, 128) || !make_map_bf16(&mga, ga, M, R, R, 128))
     return HAWK_ERR_DEVICE;
   if (cudaFuncSetAttribute(gates_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess) {
     (void)cudaGetLastError();
     return HAWK_ERR_LAUNCH;
   }
   const int per_sb = max(1, min(m_tiles, sm_count() / nsb));
-  gates_fwd_kernel<<<per_sb * nsb, G_THREADS, FWD_SMEM, st>>>(mx, mw, static_cast<__nv_bfloat16*>(gx),
-                                                              static_cast<__nv_bfloat16*>(ga), (int)M, R, nsb, m_tiles,
-                                                              wait_budget, producer_off, status);
+  gates_fwd_kernel<<<per_sb * nsb, G_THREADS, FWD_SMEM, st>>>(mx, mw, mgx, mga, nsb, m_tiles, wait_budget, producer_off,
+                                                              status);
   return launch_status();
 }
 
@@ -473,19 +512,18 @@ extern "C" int hawk_gates_bwd(const void* xc, const void* dgx, const void* dga, 
                HAWK_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int m_tiles = (int)((M + 127) / 128);
-  const auto* w2 = static_cast<const __nv_bfloat16*>(packed) + (size_t)nsb * 256 * 128;
+  const auto* w2i = static_cast<const __nv_bfloat16*>(packed) + (size_t)nsb * 256 * 128;
   {  // d input
-    CUtensorMap mgx, mga, mw;
+    CUtensorMap mgx, mga, mdx, mw;
     if (!make_map_bf16(&mgx, dgx, M, R, R, 128) || !make_map_bf16(&mga, dga, M, R, R, 128) ||
-        !make_map_bf16(&mw, w2, (long long)nsb * 128, 256, 256, 128))
+        !make_map_bf16(&mdx, dxc, M, R, R, 128) || !make_map_bf16(&mw, w2i, (long long)nsb * 128, 384, 384, 128))
       return HAWK_ERR_DEVICE;
     if (cudaFuncSetAttribute(gates_dx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DX_SMEM) != cudaSuccess) {
       (void)cudaGetLastError();
       return HAWK_ERR_LAUNCH;
     }
     const int per_sb = max(1, min(m_tiles, sm_count() / nsb));
-    gates_dx_kernel<<<per_sb * nsb, G_THREADS, DX_SMEM, st>>>(mgx, mga, mw, static_cast<__nv_bfloat16*>(dxc), (int)M, R,
-                                                              nsb, m_tiles, status);
+    gates_dx_kernel<<<per_sb * nsb, G_THREADS, DX_SMEM, st>>>(mgx, mga, mdx, mw, nsb, m_tiles, status);
     int rc = launch_status();
     if (rc != HAWK_OK) return rc;
   }
@@ -518,7 +556,7 @@ extern "C" int hawk_debug_wait_timeout(void* scratch, size_t scratch_bytes, long
                                        void* stream) {
   HAWK_REQUIRE(scratch && status, HAWK_ERR_NULL);
   HAWK_REQUIRE(budget_cycles >= 1000 && budget_cycles <= 100000000LL, HAWK_ERR_SHAPE);
-  const size_t act = (size_t)128 * 128 * 2, pk = 2 * (size_t)256 * 128 * 2;
+  const size_t act = (size_t)128 * 128 * 2, pk = (size_t)(256 * 128 + 128 * 384) * 2;
   HAWK_REQUIRE(scratch_bytes >= 3 * act + pk, HAWK_ERR_WORKSPACE);
   HAWK_REQUIRE(aligned(scratch, 256), HAWK_ERR_ALIGN);
   auto* p = static_cast<unsigned char*>(scratch);

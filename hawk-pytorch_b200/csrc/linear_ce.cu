@@ -3,16 +3,17 @@
 // [chunk, V] fp32 temporaries per chunk).
 //
 // Pipeline, all on the caller's stream:
-//   1. cast_transpose : weight [V,H], act [N,H] (fp32 or bf16) -> bf16 copies and bf16 transposes,
-//                       so that every GEMM below takes both operands K-major.
+//   1. cast           : fp32 weight [V,H] and act [N,H] -> bf16 copies (bf16 inputs are used in place).
 //   2. GEMM + softmax epilogue (tcgen05): logits tile = act @ weight^T accumulated in TMEM; the
 //      epilogue rounds it to bf16 (as F.linear does under autocast, fused_cross_entropy.py:28),
 //      stores it once, and reduces each row's tile to (max, sum exp) online, 32 columns at a time;
 //      it also picks out the label's logit.  No fp32 [N,V] tensor is ever written.
 //   3. row reduce     : tile statistics -> log-sum-exp per row, loss = mean(lse - correct) (:37-44,59-64).
-//   4. dprobs         : logits -> (softmax - onehot) / N in bf16, in place, plus its transpose (:47-52).
+//   4. dprobs         : logits -> (softmax - onehot) / N in bf16, in place (:47-52).
 //   5. two tcgen05 GEMMs with a plain fp32 epilogue: d act = dprobs @ weight (:56),
-//      d weight = dprobs^T @ act (:55).
+//      d weight = dprobs^T @ act (:55).  Neither needs a transposed copy: an operand whose contraction
+//      index is the row index of its tensor (weight in d act; dprobs and act in d weight) is read as an
+//      MN-major tile straight from the row-major tensor.
 //
 // The GEMM is one kernel: C[M,Nc] = A[M,K] . B[Nc,K]^T, bf16 operands, fp32 accumulation.
 // CTA = 128x256 output tile, K in blocks of 64 (128-byte swizzled rows).  Warp-specialised:
@@ -58,8 +59,7 @@ struct EpiParams {
   long long ldo;
 };
 
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = 256.
-constexpr uint32_t kIdesc = umma_idesc(BM, BN);
+constexpr int MN_BOX = 64 * 128;  // bytes of one [64 columns x 64 rows] box of an MN-major operand
 
 // tile index -> (m_tile, n_tile): groups of GROUP_M row tiles sweep all column tiles, so the tiles
 // in flight share a small set of A and B tiles in L2
@@ -77,9 +77,12 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 // ---------------------------------------------------------------------------------------------
 // the GEMM
 // ---------------------------------------------------------------------------------------------
-template <int MH>
+// A_MN / B_MN: the operand is read as an MN-major tile, i.e. straight from a row-major [K, M] (or [K, Nc])
+// tensor whose rows are the contraction index; its tensor map then has boxes of [64 columns x 64 rows],
+// one box per 64 M/N indices, 8192 bytes apart in the stage.
+template <int MH, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     int K, int m_tiles, int n_tiles, EpiParams ep, int* status) {
   using Cfg = GemmCfg<MH>;
   constexpr int KSTAGES = Cfg::STAGES, STAGE_BYTES_G = Cfg::STAGE_BYTES, A_BYTES = Cfg::A_BYTES, NACC = Cfg::NACC;
@@ -89,6 +92,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  constexpr uint32_t kIdescMaj = umma_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = m_tiles * n_tiles;
   const int kblocks = (K + BK - 1) / BK;
@@ -125,8 +129,18 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) break;
           mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES_G);
           unsigned char* st = smem + s * STAGE_BYTES_G;
-          tma_load_2d(st, &map_a, &full_bar[s], kb * BK, mt * BM * MH);
-          tma_load_2d(st + A_BYTES, &map_b, &full_bar[s], kb * BK, nt * BN);
+          if (A_MN) {
+#pragma unroll
+            for (int q = 0; q < 2 * MH; ++q) tma_load_2d(st + q * MN_BOX, &map_a, &full_bar[s], mt * BM * MH + q * 64, kb * BK);
+          } else {
+            tma_load_2d(st, &map_a, &full_bar[s], kb * BK, mt * BM * MH);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int q = 0; q < BN / 64; ++q) tma_load_2d(st + A_BYTES + q * MN_BOX, &map_b, &full_bar[s], nt * BN + q * 64, kb * BK);
+          } else {
+            tma_load_2d(st + A_BYTES, &map_b, &full_bar[s], kb * BK, nt * BN);
+          }
         }
       }
       // a wait gave up somewhere: let the copies issued last land before the CTA's shared memory goes
@@ -154,8 +168,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int k = 0; k < BK / UMMA_K; ++k) {
 #pragma unroll
             for (int hh = 0; hh < MH; ++hh) {  // the halves of a 256-row tile accumulate side by side in TMEM
-              umma_bf16(d_tmem + hh * BN, umma_desc_sw128(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 2),
-                        umma_desc_sw128(b_addr + k * UMMA_K * 2), kIdesc, (kb | k) ? 1u : 0u);
+              // K-major: 16 K-elements further along the 128-byte rows; MN-major: 16 K-rows (2048 bytes) further down
+              const uint64_t ad = A_MN ? umma_desc_sw128(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 128, MN_BOX)
+                                       : umma_desc_sw128(a_addr + hh * A_HALF_BYTES + k * UMMA_K * 2);
+              const uint64_t bd = B_MN ? umma_desc_sw128(b_addr + k * UMMA_K * 128, MN_BOX)
+                                       : umma_desc_sw128(b_addr + k * UMMA_K * 2);
+              umma_bf16(d_tmem + hh * BN, ad, bd, kIdescMaj, (kb | k) ? 1u : 0u);
             }
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
@@ -269,30 +287,6 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 // small kernels around the GEMMs
 // ---------------------------------------------------------------------------------------------
-// in [R, C] (fp32 or bf16, row-major) -> out [R, C] bf16 and outT [C, ldt] bf16
-template <typename TI>
-__global__ void __launch_bounds__(256)
-cast_transpose_kernel(const TI* __restrict__ in, __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ outT,
-                      int R, int C, long long ldt) {
-  __shared__ __nv_bfloat16 tile[64][66];
-  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
-  for (int i = ty; i < 64; i += 4) {
-    const int r = r0 + i, c = c0 + tx;
-    __nv_bfloat16 v = __float2bfloat16(0.f);
-    if (r < R && c < C) {
-      v = __float2bfloat16((float)in[(long long)r * C + c]);
-      out[(long long)r * C + c] = v;
-    }
-    tile[i][tx] = v;
-  }
-  __syncthreads();
-  for (int i = ty; i < 64; i += 4) {
-    const int c = c0 + i, r = r0 + tx;
-    if (c < C && r < R) outT[(long long)c * ldt + r] = tile[tx][i];
-  }
-}
-
 // stats [n_tiles, N] -> lse [N]; per-block partial sums of (lse - correct) -> partial [gridDim.x]
 __global__ void __launch_bounds__(256)
 ce_row_reduce_kernel(const float2* __restrict__ stats, const float* __restrict__ correct, float* __restrict__ lse,
@@ -341,97 +335,67 @@ __global__ void ce_poison_on_abort_kernel(const int* __restrict__ status, float*
   if (*status != 0) *loss = __int_as_float(0x7fc00000);
 }
 
-// logits [N, ldl] bf16 -> dprobs = (exp(logit - lse) - onehot) / N, in place, and its transpose [V, ldt].
-// 64x64 tiles through shared memory; interior tiles move 16 bytes per thread in both directions.
+// logits [N, ldl] bf16 -> dprobs = (exp(logit - lse) - onehot) / N, in place.  One CTA per row, 16 bytes
+// per thread per step.
 __global__ void __launch_bounds__(256)
-ce_dprobs_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, __nv_bfloat16* __restrict__ dpT, long long ldt,
-                 const float* __restrict__ lse, const long long* __restrict__ labels, int N, int V, float inv_n) {
-  __shared__ __nv_bfloat16 tile[64][66];
-  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-  const bool interior = r0 + 64 <= N && c0 + 64 <= V && (ldl % 8) == 0 && (ldt % 8) == 0;
-  if (interior) {
-    const int c8 = (threadIdx.x & 7) * 8;
+ce_dprobs_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const float* __restrict__ lse,
+                 const long long* __restrict__ labels, int N, int V, float inv_n) {
+  const int r = blockIdx.x;
+  if (r >= N) return;
+  __nv_bfloat16* row = logits + (long long)r * ldl;
+  const float l = lse[r];
+  const long long label = labels[r];
+  const int nvec = (ldl % 8 == 0) ? V / 8 : 0;
+  for (int jv = threadIdx.x; jv < nvec; jv += blockDim.x) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + jv * 8);
+    const int lab = (int)(label - (long long)jv * 8);  // 0..7 when the label is in this vector
+    const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t out[4];
 #pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      const int i = pass * 32 + (threadIdx.x >> 3);
-      const int r = r0 + i;
-      __nv_bfloat16* src = logits + (long long)r * ldl + c0 + c8;
-      const uint4 raw = *reinterpret_cast<const uint4*>(src);
-      const float l = lse[r];
-      const int lab = (int)(labels[r] - (long long)(c0 + c8));  // 0..7 when the label is in this vector
-      const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
-      uint32_t out[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 f = unpack_bf16x2(in[q]);
-        float p0 = __expf(f.x - l), p1 = __expf(f.y - l);
-        if (lab == 2 * q) p0 -= 1.f;
-        if (lab == 2 * q + 1) p1 -= 1.f;
-        out[q] = pack_bf16x2(p0 * inv_n, p1 * inv_n);
-        *reinterpret_cast<uint32_t*>(&tile[i][c8 + 2 * q]) = out[q];
-      }
-      *reinterpret_cast<uint4*>(src) = make_uint4(out[0], out[1], out[2], out[3]);
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = unpack_bf16x2(in[q]);
+      float p0 = __expf(f.x - l), p1 = __expf(f.y - l);
+      if (lab == 2 * q) p0 -= 1.f;
+      if (lab == 2 * q + 1) p1 -= 1.f;
+      out[q] = pack_bf16x2(p0 * inv_n, p1 * inv_n);
     }
-    __syncthreads();
-    const int r8 = (threadIdx.x & 7) * 8;
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      const int c = pass * 32 + (threadIdx.x >> 3);
-      uint32_t o[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t lo = *reinterpret_cast<const unsigned short*>(&tile[r8 + 2 * q][c]);
-        const uint32_t hi = *reinterpret_cast<const unsigned short*>(&tile[r8 + 2 * q + 1][c]);
-        o[q] = lo | (hi << 16);
-      }
-      *reinterpret_cast<uint4*>(dpT + (long long)(c0 + c) * ldt + r0 + r8) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-    return;
+    *reinterpret_cast<uint4*>(row + jv * 8) = make_uint4(out[0], out[1], out[2], out[3]);
   }
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  for (int i = ty; i < 64; i += 4) {
-    const int r = r0 + i, c = c0 + tx;
-    __nv_bfloat16 v = __float2bfloat16(0.f);
-    if (r < N && c < V) {
-      const float lg = __bfloat162float(logits[(long long)r * ldl + c]);
-      float p = __expf(lg - lse[r]);
-      if ((long long)c == labels[r]) p -= 1.f;
-      v = __float2bfloat16(p * inv_n);
-      logits[(long long)r * ldl + c] = v;
-    }
-    tile[i][tx] = v;
-  }
-  __syncthreads();
-  for (int i = ty; i < 64; i += 4) {
-    const int c = c0 + i, r = r0 + tx;
-    if (c < V && r < N) dpT[(long long)c * ldt + r] = tile[tx][i];
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += blockDim.x) {
+    float p = __expf(__bfloat162float(row[c]) - l);
+    if ((long long)c == label) p -= 1.f;
+    row[c] = __float2bfloat16(p * inv_n);
   }
 }
 
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-// C[M, Nc] = A[M, K] . B[Nc, K]^T  (A, B bf16 row-major with pitches lda, ldb)
-template <int MH>
+// C[M, Nc] = A . B^T with bf16 operands.  A K-major operand is a row-major [M, K] (or [Nc, K]) tensor; an
+// MN-major operand (A_MN / B_MN) is a row-major [K, M] (or [K, Nc]) tensor.  lda / ldb: row pitches.
+template <int MH, bool A_MN, bool B_MN>
 static int launch_gemm(const __nv_bfloat16* A, long long lda, const __nv_bfloat16* B, long long ldb, int M, int Nc, int K,
                        const EpiParams& ep, int* status, cudaStream_t st) {
   using Cfg = GemmCfg<MH>;
   CUtensorMap ma, mb;
-  if (!make_map_bf16(&ma, A, M, K, lda, BM * MH) || !make_map_bf16(&mb, B, Nc, K, ldb, BN)) return HAWK_ERR_DEVICE;
+  const bool oka = A_MN ? make_map_bf16(&ma, A, K, M, lda, 64) : make_map_bf16(&ma, A, M, K, lda, BM * MH);
+  const bool okb = B_MN ? make_map_bf16(&mb, B, K, Nc, ldb, 64) : make_map_bf16(&mb, B, Nc, K, ldb, BN);
+  if (!oka || !okb) return HAWK_ERR_DEVICE;
+  auto kern = gemm_bf16_kernel<MH, A_MN, B_MN>;
   // per call: the attribute belongs to the current device's copy of the kernel
-  if (cudaFuncSetAttribute(gemm_bf16_tn_kernel<MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
     (void)cudaGetLastError();
     return HAWK_ERR_LAUNCH;
   }
   const int m_tiles = (M + BM * MH - 1) / (BM * MH), n_tiles = (Nc + BN - 1) / BN;
   const int grid = min(m_tiles * n_tiles, sm_count());
-  gemm_bf16_tn_kernel<MH><<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ma, mb, K, m_tiles, n_tiles, ep, status);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM, st>>>(ma, mb, K, m_tiles, n_tiles, ep, status);
   return launch_status();
 }
 
 struct CeLayout {  // carve-up of the workspace (all offsets 256-byte aligned)
-  size_t wb, wbT, ab, abT, logits, dpT, stats, correct, lse, partial, status, total;
-  long long ldV, ldN;
+  size_t wb, ab, logits, stats, correct, lse, partial, total;
+  long long ldV;
   int n_tiles, n_blocks;
 };
 
@@ -440,21 +404,16 @@ static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 static CeLayout ce_layout(long long N, long long H, long long V) {
   CeLayout L;
   L.ldV = (V + 7) & ~7LL;
-  L.ldN = (N + 7) & ~7LL;
   L.n_tiles = (int)((V + BN - 1) / BN);
   L.n_blocks = (int)((N + 255) / 256);
   size_t o = 0;
-  L.wb = o;      o += up256((size_t)V * H * 2);
-  L.wbT = o;     o += up256((size_t)H * L.ldV * 2);
+  L.wb = o;      o += up256((size_t)V * H * 2);   // bf16 copies of fp32 operands (unused for bf16 inputs)
   L.ab = o;      o += up256((size_t)N * H * 2);
-  L.abT = o;     o += up256((size_t)H * L.ldN * 2);
   L.logits = o;  o += up256((size_t)N * L.ldV * 2);
-  L.dpT = o;     o += up256((size_t)V * L.ldN * 2);
   L.stats = o;   o += up256((size_t)L.n_tiles * N * sizeof(float2));
   L.correct = o; o += up256((size_t)N * 4);
   L.lse = o;     o += up256((size_t)N * 4);
   L.partial = o; o += up256((size_t)L.n_blocks * 4);
-  L.status = o;  o += 256;
   L.total = o;
   return L;
 }
@@ -482,29 +441,24 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
                HAWK_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
-  auto* wb = reinterpret_cast<__nv_bfloat16*>(ws + L.wb);
-  auto* wbT = reinterpret_cast<__nv_bfloat16*>(ws + L.wbT);
-  auto* ab = reinterpret_cast<__nv_bfloat16*>(ws + L.ab);
-  auto* abT = reinterpret_cast<__nv_bfloat16*>(ws + L.abT);
   auto* logits = reinterpret_cast<__nv_bfloat16*>(ws + L.logits);
-  auto* dpT = reinterpret_cast<__nv_bfloat16*>(ws + L.dpT);
   auto* stats = reinterpret_cast<float2*>(ws + L.stats);
   auto* correct = reinterpret_cast<float*>(ws + L.correct);
   auto* lse = reinterpret_cast<float*>(ws + L.lse);
   auto* partial = reinterpret_cast<float*>(ws + L.partial);
 
-  // 1. operands in bf16, both orientations
-  {
-    dim3 gw((unsigned)((H + 63) / 64), (unsigned)((V + 63) / 64)), ga((unsigned)((H + 63) / 64), (unsigned)((N + 63) / 64));
-    if (dtype == HAWK_F32) {
-      cast_transpose_kernel<float><<<gw, 256, 0, st>>>(static_cast<const float*>(weight), wb, wbT, (int)V, (int)H, L.ldV);
-      cast_transpose_kernel<float><<<ga, 256, 0, st>>>(static_cast<const float*>(act), ab, abT, (int)N, (int)H, L.ldN);
-    } else {
-      cast_transpose_kernel<__nv_bfloat16><<<gw, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(weight), wb, wbT, (int)V, (int)H, L.ldV);
-      cast_transpose_kernel<__nv_bfloat16><<<ga, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(act), ab, abT, (int)N, (int)H, L.ldN);
-    }
-    int rc = launch_status();
+  // 1. operands in bf16 (row-major, as given: no transposes)
+  const __nv_bfloat16* wb = static_cast<const __nv_bfloat16*>(weight);
+  const __nv_bfloat16* ab = static_cast<const __nv_bfloat16*>(act);
+  if (dtype == HAWK_F32) {
+    auto* wcast = reinterpret_cast<__nv_bfloat16*>(ws + L.wb);
+    auto* acast = reinterpret_cast<__nv_bfloat16*>(ws + L.ab);
+    int rc = hawk_cast_f32_bf16(static_cast<const float*>(weight), wcast, V * H, stream);
     if (rc != HAWK_OK) return rc;
+    rc = hawk_cast_f32_bf16(static_cast<const float*>(act), acast, N * H, stream);
+    if (rc != HAWK_OK) return rc;
+    wb = wcast;
+    ab = acast;
   }
   // 2. logits + online softmax statistics.  The label's logit is written by the tile that holds the label;
   // a label outside [0, V) matches no tile, so its slot keeps this NaN pattern and the loss comes out NaN
@@ -523,21 +477,21 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     ep.stats = stats;
     ep.correct = correct;
     ep.labels = reinterpret_cast<const long long*>(labels);
-    int rc = launch_gemm<1>(ab, H, wb, H, (int)N, (int)V, (int)H, ep, status, st);
+    int rc = launch_gemm<1, false, false>(ab, H, wb, H, (int)N, (int)V, (int)H, ep, status, st);
     if (rc != HAWK_OK) return rc;
   }
   // 3. log-sum-exp per row and the mean loss
   ce_row_reduce_kernel<<<L.n_blocks, 256, 0, st>>>(stats, correct, lse, partial, (int)N, L.n_tiles);
   ce_loss_final_kernel<<<1, 256, 0, st>>>(partial, L.n_blocks, 1.0f / (float)N, loss);
-  // 4. dprobs in place + transpose
+  // 4. dprobs in place
+  ce_dprobs_kernel<<<(unsigned)N, 256, 0, st>>>(logits, L.ldV, lse, reinterpret_cast<const long long*>(labels), (int)N,
+                                                (int)V, 1.0f / (float)N);
   {
-    dim3 g((unsigned)((V + 63) / 64), (unsigned)((N + 63) / 64));
-    ce_dprobs_kernel<<<g, 256, 0, st>>>(logits, L.ldV, dpT, L.ldN, lse, reinterpret_cast<const long long*>(labels),
-                                        (int)N, (int)V, 1.0f / (float)N);
     int rc = launch_status();
     if (rc != HAWK_OK) return rc;
   }
-  // 5. d act = dprobs @ W ; d weight = dprobs^T @ act
+  // 5. d act [N,H] = dprobs [N,V] . W [V,H]   : A K-major (dprobs rows), B MN-major (W's rows are the K index)
+  //    d weight [V,H] = dprobs^T . act [N,H]  : A and B MN-major (the rows of dprobs and act are the K index)
   {
     EpiParams ep{};
     ep.mode = EPI_F32;
@@ -545,11 +499,11 @@ extern "C" int hawk_linear_ce_fwd_bwd(const void* weight, const void* act, const
     ep.Nc = (int)H;
     ep.out = dact;
     ep.ldo = H;
-    int rc = launch_gemm<2>(logits, L.ldV, wbT, L.ldV, (int)N, (int)H, (int)V, ep, status, st);
+    int rc = launch_gemm<2, false, true>(logits, L.ldV, wb, H, (int)N, (int)H, (int)V, ep, status, st);
     if (rc != HAWK_OK) return rc;
     ep.M = (int)V;
     ep.out = dweight;
-    rc = launch_gemm<2>(dpT, L.ldN, abT, L.ldN, (int)V, (int)H, (int)N, ep, status, st);
+    rc = launch_gemm<2, true, true>(logits, L.ldV, ab, H, (int)V, (int)H, (int)N, ep, status, st);
     if (rc != HAWK_OK) return rc;
   }
   ce_poison_on_abort_kernel<<<1, 1, 0, st>>>(status, loss);

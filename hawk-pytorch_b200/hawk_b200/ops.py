@@ -563,7 +563,7 @@ def linear_ce(weight: torch.Tensor, act: torch.Tensor, labels: torch.Tensor) -> 
     dact = torch.empty(N, H, dtype=torch.float32, device=act.device)
     ws_bytes = lib.hawk_linear_ce_workspace_bytes(N, H, V)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=act.device)
-    with _on(act, "linear_ce", 8):
+    with _on(act, "linear_ce", 9 if weight.dtype == torch.float32 else 7):
         _lib.check(lib.hawk_linear_ce_fwd_bwd(weight.data_ptr(), act.data_ptr(), labels.data_ptr(), loss.data_ptr(),
                                               dweight.data_ptr(), dact.data_ptr(), ws.data_ptr(), ws_bytes, N, H, V,
                                               _dt(weight), _status_word(act.device).data_ptr(), _stream(act)),
@@ -919,7 +919,7 @@ def gates_pack(wx: torch.Tensor, wa: torch.Tensor) -> torch.Tensor:
 @gates_pack.register_fake
 def _(wx, wa):
     nb, bw, _ = wx.shape
-    return wx.new_empty(2 * (nb * bw // 128) * 256 * 128, dtype=torch.bfloat16)
+    return wx.new_empty((nb * bw // 128) * (256 * 128 + 128 * 384), dtype=torch.bfloat16)
 
 
 @torch.library.custom_op("hawk_b200::gates_fwd", mutates_args=())

@@ -170,7 +170,8 @@ int hawk_decode_block_step(const void* xy, int64_t xy_row_stride, void* conv_sta
  * Arithmetic is what the reference does under bf16 autocast: bf16 operands, fp32 accumulation,
  * logits rounded to bf16, softmax in fp32, dprobs rounded to bf16 before the gradient GEMMs.
  * H must be a multiple of 8.  Workspace: hawk_linear_ce_workspace_bytes(N, H, V), 256-byte aligned
- * (bf16 operand copies, the [N,V] bf16 logits/dprobs buffer and its transpose, row statistics).
+ * (bf16 copies of fp32 operands, the [N,V] bf16 logits/dprobs buffer, row statistics; no transposed
+ * copies: the gradient GEMMs read their row-contracted operands as MN-major tiles).
  * status: one int32 in device memory, zeroed by the caller once; a kernel whose bounded wait on an
  * mbarrier ran out sets it to 1 (the results of that call are then invalid) instead of hanging, and the
  * call then also overwrites `loss` with NaN, so a caller that never reads the status word still sees it.
@@ -212,7 +213,7 @@ int hawk_gates_bwd(const void* xc, const void* dgx, const void* dga, const void*
                    void* stream);
 
 /* Shows that a device-side wait of the tcgen05 kernels gives up instead of hanging (no counterpart in
- * the reference): launches one 128 x 128 tile of the gate-projection kernel inside `scratch` (>= 229376
+ * the reference): launches one 128 x 128 tile of the gate-projection kernel inside `scratch` (>= 262144
  * bytes, 256-byte aligned) with its TMA producer switched off and a wait budget of `budget_cycles` clock
  * cycles (1e3 .. 1e8).  The kernel must return by itself and set *status to 1. */
 int hawk_debug_wait_timeout(void* scratch, size_t scratch_bytes, long long budget_cycles, int* status,

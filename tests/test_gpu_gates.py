@@ -103,7 +103,7 @@ def test_device_side_wait_gives_up_and_reports():
     from hawk_b200 import _lib, ops
     lib = _lib.load()
     dev = torch.device("cuda:0")
-    scratch = torch.zeros(229376, dtype=torch.uint8, device=dev)
+    scratch = torch.zeros(262144, dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     rc = lib.hawk_debug_wait_timeout(scratch.data_ptr(), scratch.numel(), 100000, status.data_ptr(),
                                      torch.cuda.current_stream().cuda_stream)
