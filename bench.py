@@ -14,7 +14,9 @@ One JSON line is printed by rank 0:
   roofline   the RG-LRU scan forward+backward launches of the step: algorithmic bytes over the mean
              CUDA-event time of those launches INSIDE the timed training steps, against the measured HBM
              copy bandwidth of this pool (MEASURED_PEAKS.json, else the 6650 GB/s fallback);
-             `isolated` repeats the measurement on the plain scan (24 B/element) outside the step (N = 1);
+             `isolated` / `isolated_fused` repeat the measurement outside the step on the plain scan
+             (24 B/element) and on the fused entry points (N = 1);
+  comm       (N > 1) the gradient all-reduces of one step timed per DDP bucket against the backward pass;
   kernels    mean device time and derived rate of each of this library's entry points, from separate
              instrumented steps after the timed regions;
   parity     the check that is free at the reference initialisation: first-step loss = ln 32000 and only
@@ -449,7 +451,8 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
-    trainer = train.Trainer(M.hawk_1b_config(), dev, seed=0, world_size=world)
+    timeline = train.CommTimeline() if world > 1 else None
+    trainer = train.Trainer(M.hawk_1b_config(), dev, seed=0, world_size=world, timeline=timeline)
     g = torch.Generator().manual_seed(1234 + rank)
     n_host = warmup + steps
     host_ids = torch.randint(1, VOCAB, (n_host, B_PER_GPU, SEQ_LEN), generator=g).pin_memory()
@@ -512,6 +515,7 @@ def run_ours(args):
     barrier()
     kernel_ms = {k: ops.LOG.mean_ms(k) for k in ops.LOG.events}
     ops.LOG.reset(enabled=False)
+    comm = timeline.summary() if timeline is not None else None  # the gradient all-reduces of the last step
 
     if rank != 0:
         return 0
@@ -533,15 +537,16 @@ def run_ours(args):
             ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, gb, h, xs[3])
         torch.cuda.synchronize()
         time.sleep(3.0)  # let the board leave the power-capped state of the training loop: a burst figure
-        ops.LOG.reset(enabled=True, timed=True)
-        for _ in range(20):
-            ops.scan_fwd(xs[0], xs[1], xs[2], lam, None, gb)
-        for _ in range(20):
-            ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, gb, h, xs[3])
-        torch.cuda.synchronize()
-        isolated = {"fwd_ms": ops.LOG.mean_ms("scan_fwd"), "bwd_ms": ops.LOG.mean_ms("scan_bwd")}
-        ops.LOG.reset(enabled=False)
-        del xs, h
+        isolated = {"fwd_ms": _median_ms(lambda: ops.scan_fwd(xs[0], xs[1], xs[2], lam, None, gb), 20, 5),
+                    "bwd_ms": _median_ms(lambda: ops.scan_bwd(xs[0], xs[1], xs[2], lam, None, gb, h, xs[3]), 20, 5)}
+        # the fused entry points the step launches, alone in the same state
+        xy = torch.randn(B_PER_GPU, SEQ_LEN, 4096, generator=g2, device=dev).bfloat16()
+        dxy = torch.empty_like(xy)
+        hh, _ = ops.scan_gelu_fwd(xs[0], xs[1], xs[2], lam, gb, xy[..., 2048:])
+        isolated["fused_fwd_ms"] = _median_ms(lambda: ops.scan_gelu_fwd(xs[0], xs[1], xs[2], lam, gb, xy[..., 2048:]), 20, 5)
+        isolated["fused_bwd_ms"] = _median_ms(
+            lambda: ops.scan_gelu_bwd_into(xs[0], xs[1], xs[2], lam, gb, hh, xy[..., 2048:], xs[3], dxy[..., 2048:]), 20, 5)
+        del xs, h, hh, xy, dxy
 
     # bytes each launch must move: [bytes per element forward, backward] of the entry points the step uses
     fwd_name, bwd_name = scan_names
@@ -560,8 +565,12 @@ def run_ours(args):
         t = (isolated["fwd_ms"] + isolated["bwd_ms"]) * 1e-3
         roofline["isolated"] = {"achieved": 24 * n_elem / t / 1e9, "frac": 24 * n_elem / t / 1e9 / hbm_peak,
                                 "launch_ms": {"fwd": isolated["fwd_ms"], "bwd": isolated["bwd_ms"]},
-                                "note": "scan_fwd + scan_bwd (24 B/element), same shape, 20 back-to-back launches each "
-                                        "outside the step, after 3 s idle (burst clocks)"}
+                                "note": "scan_fwd + scan_bwd (24 B/element), same shape, median of 20 back-to-back "
+                                        "launches each outside the step, after 3 s idle (burst clocks)"}
+        tf = (isolated["fused_fwd_ms"] + isolated["fused_bwd_ms"]) * 1e-3
+        roofline["isolated_fused"] = {"achieved": 32 * n_elem / tf / 1e9, "frac": 32 * n_elem / tf / 1e9 / hbm_peak,
+                                      "launch_ms": {"fwd": isolated["fused_fwd_ms"], "bwd": isolated["fused_bwd_ms"]},
+                                      "note": "scan_gelu_fwd + scan_gelu_bwd (32 B/element), measured the same way"}
     kernels = {}
     n_ce = B_PER_GPU * (SEQ_LEN - 1)
     rates = {"conv1d_fwd": (4 * n_elem, "GB/s"), "conv1d_bwd": (6 * n_elem, "GB/s"),
@@ -590,6 +599,11 @@ def run_ours(args):
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / steps, "last_loss": last},
         "gpu_launches": launches, "roofline": roofline, "kernels": kernels, "clocks": clocks, "parity": parity,
     }
+    if comm is not None:
+        comm["what"] = ("gradient all-reduce per DDP bucket in one step on rank 0: time from the bucket being ready on the "
+                        "compute stream to its all-reduce being done, and how far the last all-reduce ran past the moment "
+                        "the last bucket was ready (communication the backward pass did not hide)")
+        line["comm"] = comm
 
     if world == 1:
         del trainer, dev_ids

@@ -966,6 +966,49 @@ def _(xc, dgx, dga, packed, dxc, bw):
     return (xc.new_empty(nb, bw, bw, dtype=torch.float32), xc.new_empty(nb, bw, bw, dtype=torch.float32))
 
 
+# The strided-batch cuBLAS form of the same two projections for the cases the kernels do not take (fp32
+# activations, widths that are not multiples of 128), as opaque operators so that torch.compile traces
+# through the recurrent core without looking inside.
+@torch.library.custom_op("hawk_b200::gates_bmm_fwd", mutates_args=())
+def gates_bmm_fwd(xc: torch.Tensor, wx: torch.Tensor, wa: torch.Tensor) -> torch.Tensor:
+    """[2, M, R] from xc [M, R] and weights [nb, bw, bw] already in xc's dtype; reads and writes the final
+    layout in place (batch stride bw, row pitch R): no transposed copies."""
+    M, R = xc.shape
+    nb, bw, _ = wx.shape
+    out = torch.empty(2, M, R, dtype=xc.dtype, device=xc.device)
+    xb = xc.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
+    torch.bmm(xb, wx, out=out[0].view(M, nb, bw).transpose(0, 1))
+    torch.bmm(xb, wa, out=out[1].view(M, nb, bw).transpose(0, 1))
+    return out
+
+
+@gates_bmm_fwd.register_fake
+def _(xc, wx, wa):
+    return xc.new_empty(2, xc.shape[0], xc.shape[1])
+
+
+@torch.library.custom_op("hawk_b200::gates_bmm_bwd_into", mutates_args=("dxc",))
+def gates_bmm_bwd_into(xc: torch.Tensor, dgx: torch.Tensor, dga: torch.Tensor, wx: torch.Tensor, wa: torch.Tensor,
+                       dxc: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """dxc += dgx Wx^T + dga Wa^T in place; returns (dwx, dwa) in the weights' dtype."""
+    M, R = xc.shape
+    nb, bw, _ = wx.shape
+    gxb = dgx.view(M, nb, bw).transpose(0, 1)
+    gab = dga.view(M, nb, bw).transpose(0, 1)
+    xT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
+    dwx = torch.bmm(xT, gxb)
+    dwa = torch.bmm(xT, gab)
+    dxb = dxc.view(M, nb, bw).transpose(0, 1)
+    torch.baddbmm(dxb, gxb, wx.transpose(1, 2), out=dxb)
+    torch.baddbmm(dxb, gab, wa.transpose(1, 2), out=dxb)
+    return dwx, dwa
+
+
+@gates_bmm_bwd_into.register_fake
+def _(xc, dgx, dga, wx, wa, dxc):
+    return wx.new_empty(wx.shape), wx.new_empty(wx.shape)
+
+
 class _FusedGates(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, wx, wa):
@@ -1077,7 +1120,8 @@ class _RecurrentCore(torch.autograd.Function):
         R = xy.shape[-1] // 2
         nb, bw, _ = wx.shape
         with torch.autocast("cuda", enabled=False):
-            if _conv_view(xy) is not xy:
+            # strides only (traceable by torch.compile); the operators below copy a misaligned view themselves
+            if not (xy.stride(-1) == 1 and xy.stride(-2) % 8 == 0 and xy.stride(0) % 8 == 0 and xy.dim() == 3):
                 xy = xy.contiguous()
             xb, y = xy[..., :R], xy[..., R:]
             dt = xy.dtype
@@ -1089,11 +1133,8 @@ class _RecurrentCore(torch.autograd.Function):
                 wac = wxc
                 gates = gates_fwd(xc.view(M, R), wxc, bw)
             else:      # strided-batch cuBLAS GEMMs on the final layout
-                gates = torch.empty(2, M, R, dtype=dt, device=xy.device)
                 wxc, wac = wx.to(dt), wa.to(dt)
-                xcb = xc.view(M, nb, bw).transpose(0, 1)  # [nb, M, bw] view
-                torch.bmm(xcb, wxc, out=gates[0].view(M, nb, bw).transpose(0, 1))
-                torch.bmm(xcb, wac, out=gates[1].view(M, nb, bw).transpose(0, 1))
+                gates = gates_bmm_fwd(xc.view(M, R), wxc, wac)
             gx, ga = gates[0].view(xc.shape), gates[1].view(xc.shape)
             h, out = scan_gelu_fwd(xc, gx, ga, lam, gate_bias, y)  # scan and gelu(y) * h in one kernel
         ctx.save_for_backward(xy, conv_w, xc, wxc, wac, gx, ga, lam, gate_bias, h)
@@ -1117,14 +1158,7 @@ class _RecurrentCore(torch.autograd.Function):
             if fused:  # d xc (scan) += d gx Wx^T + d ga Wa^T in place, and both weight gradients
                 dwx, dwa = gates_bwd_into(xc.view(M, R), dgx.view(M, R), dga.view(M, R), wxc, dxc.view(M, R), bw)
             else:
-                gxb = dgx.view(M, nb, bw).transpose(0, 1)
-                gab = dga.view(M, nb, bw).transpose(0, 1)
-                xcT = xc.view(M, nb, bw).permute(1, 2, 0)  # [nb, bw, M] view
-                dwx = torch.bmm(xcT, gxb)
-                dwa = torch.bmm(xcT, gab)
-                dxcb = dxc.view(M, nb, bw).transpose(0, 1)
-                torch.baddbmm(dxcb, gxb, wxc.transpose(1, 2), out=dxcb)
-                torch.baddbmm(dxcb, gab, wac.transpose(1, 2), out=dxcb)
+                dwx, dwa = gates_bmm_bwd_into(xc.view(M, R), dgx.view(M, R), dga.view(M, R), wxc, wac, dxc.view(M, R))
             dcw, dcb = conv1d_bwd_into(dxc, xb, conv_w, dxy[..., :R])
         return dxy, dcw.to(cwdt), dcb.to(cbdt), dwx.to(wdt), dwa.to(wdt), dgb, dlam
 

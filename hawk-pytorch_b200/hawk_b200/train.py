@@ -120,21 +120,79 @@ class FusedAdamW(torch.optim.Optimizer):
                 self._bind(p, st)
 
 
+class CommTimeline:
+    """Times the gradient all-reduce of every DDP bucket against the backward pass (CUDA events): when the
+    bucket became ready on the compute stream, when its all-reduce finished on the communication stream.
+    `summary()` after a step gives how long the all-reduces were in flight and how far the last one ran past
+    the moment the last bucket became ready, i.e. past the end of the backward computation (the part of the
+    communication the step could not hide; DDP makes the compute stream wait for it before the optimiser)."""
+
+    def __init__(self):
+        self.ready = []        # ready events in the order the buckets were handed over
+        self.records = []      # (bucket index, bytes, ready event, done event)
+
+    def reset(self):
+        self.ready, self.records = [], []
+
+    def summary(self):
+        torch.cuda.synchronize()
+        if not self.records:
+            return None
+        first, last = self.ready[0], self.ready[-1]
+        spans = [r[2].elapsed_time(r[3]) for r in self.records]
+        return {"buckets": len(self.records), "bytes": sum(r[1] for r in self.records),
+                "ready_to_done_ms": {"max": max(spans), "sum": sum(spans)},
+                "first_to_last_bucket_ready_ms": first.elapsed_time(last),
+                "exposed_tail_ms": max(0.0, max(last.elapsed_time(r[3]) for r in self.records))}
+
+
+def _comm_hook(timeline: Optional[CommTimeline], compress_bf16: bool):
+    """DDP communication hook: the default all-reduce (averaging), optionally in bf16, optionally timed."""
+    from torch.distributed.algorithms.ddp_comm_hooks import default_hooks
+
+    def hook(state, bucket):
+        if timeline is not None:
+            ready = torch.cuda.Event(enable_timing=True)
+            ready.record()
+            timeline.ready.append(ready)
+            nbytes = bucket.buffer().numel() * bucket.buffer().element_size()
+            index = bucket.index()
+        fut = (default_hooks.bf16_compress_hook if compress_bf16 else default_hooks.allreduce_hook)(state, bucket)
+        if timeline is None:
+            return fut
+
+        def done(f):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()  # runs with the communication stream current, after the bucket's all-reduce
+            timeline.records.append((index, nbytes, ready, ev))
+            return f.value()[0]
+        return fut.then(done)
+    return hook
+
+
 class Trainer:
     """Model + AdamW (+ DDP when world_size > 1).  `step(ids)` runs forward (bf16 autocast, fused
-    cross-entropy with labels = inputs), backward, gradient all-reduce and the optimiser update."""
+    cross-entropy with labels = inputs), backward, gradient all-reduce and the optimiser update.
+    `grad_comm_dtype`: torch.float32 (default: the gradients are all-reduced as they are) or torch.bfloat16
+    (each bucket is rounded to bf16 for the all-reduce and restored: half the NVLink bytes).
+    `timeline`: a CommTimeline that the step fills (multi-GPU only)."""
 
     def __init__(self, config: HawkConfig, device, seed: int = 0, lr: float = 3e-4, world_size: int = 1,
-                 autocast: bool = True, bucket_cap_mb: int = 256):
+                 autocast: bool = True, bucket_cap_mb: int = 256, grad_comm_dtype: torch.dtype = torch.float32,
+                 timeline: Optional[CommTimeline] = None):
         torch.manual_seed(seed)  # same seed on every rank: identical replicas
         self.device = torch.device(device)
         self.model = HawkModel(config).to(self.device)
         self.autocast = autocast and self.device.type == "cuda"
         self.ddp = None
+        self.timeline = timeline if world_size > 1 else None
         if world_size > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
             ids = [self.device.index] if self.device.type == "cuda" else None
             self.ddp = DDP(self.model, device_ids=ids, gradient_as_bucket_view=True, bucket_cap_mb=bucket_cap_mb)
+            assert grad_comm_dtype in (torch.float32, torch.bfloat16)
+            if self.device.type == "cuda" and (self.timeline is not None or grad_comm_dtype == torch.bfloat16):
+                self.ddp.register_comm_hook(None, _comm_hook(self.timeline, grad_comm_dtype == torch.bfloat16))
         if self.device.type == "cuda":
             from .model import Linear
             shadows = [m for m in self.model.modules() if isinstance(m, Linear) and m.bias is None] if self.autocast else []
@@ -149,6 +207,8 @@ class Trainer:
         net = self.ddp if self.ddp is not None else self.model
         with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast):
             loss = net(ids, ids)
+        if self.timeline is not None:
+            self.timeline.reset()
         loss.backward()
         if after_backward is not None:
             after_backward(loss.detach())

@@ -38,8 +38,10 @@ def test_model_loss_and_grads_match_reference_fixture(autocast):
     loss.backward()
     for k, p in model.named_parameters():
         ref = g["grad/" + k]
-        # every parameter family (scan, conv, gates, projections, norms, embedding) gets a gradient
-        assert rel_l2(p.grad.cpu(), ref) <= (5 * TOL if autocast else TOL), (k, rel_l2(p.grad.cpu(), ref))
+        # every parameter family (scan, conv, gates, projections, norms, embedding) gets a gradient.  Measured
+        # on B200: worst parameter 1.5e-2 under bf16 autocast (input_norm.weight), 3.1e-3 with fp32 activations
+        # (only the cross-entropy GEMMs are bf16 there)
+        assert rel_l2(p.grad.cpu(), ref) <= (TOL if autocast else 5e-3), (k, rel_l2(p.grad.cpu(), ref))
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
         logits = model(ids)
     assert rel_l2(logits.float().cpu(), g["logits_dezero"]) <= TOL
@@ -123,8 +125,16 @@ def test_optimiser_trajectory_matches_oracle():
     assert cl[-1] < cl[0]
     for a, b in zip(gl, cl):
         assert abs(a - b) <= TOL * b, (gl, cl)
-    moved = float((model.layers[0].recc.rg_lru_a_param.detach().cpu() - _sd(g)["layers.0.recc.rg_lru_a_param"]).abs().max())
-    assert moved >= 0.0
+    # by step 4 every parameter has moved (Adam's normalised update is ~lr per step once a gradient arrives:
+    # measured 4.0e-3 .. 1.2e-2), and it moved where the oracle's copy moved (measured cosine >= 0.98)
+    torch.manual_seed(0)
+    start = {k: v.detach().clone() for k, v in M.HawkModel(cfg).state_dict().items()}
+    for k, p in model.named_parameters():
+        dg = (p.detach().cpu() - start[k]).double().flatten()
+        dc = (sd[k].detach() - start[k]).double().flatten()
+        assert float(dg.abs().max()) >= 2e-3, (k, float(dg.abs().max()))
+        cos = float((dg @ dc) / (dg.norm() * dc.norm()))
+        assert cos >= 0.95, (k, cos)
 
 
 def test_cached_decode_matches_reference_fixture():
@@ -166,20 +176,34 @@ def test_batched_decode_matches_full_forward():
             assert rel_l2(logits[:, 0], want[:, t]) <= 1e-4, t
 
 
-def test_torch_compile_runs_the_custom_ops():
+def _inductor_usable():
+    """Whether torch.compile can build a trivial CUDA function on this machine (compiler toolchain present)."""
+    try:
+        f = torch.compile(lambda a: torch.sin(a) * 2 + 1)
+        f(torch.ones(8, device="cuda"))
+        return True
+    except Exception:  # noqa: BLE001
+        return False
+
+
+def test_torch_compile_fullgraph_traces_through_the_custom_ops():
+    """torch.compile(model, fullgraph=True): any graph break inside this library's operators (custom ops,
+    the recurrent-core / linear autograd Functions) is an error here, not a silent fallback.  Skipped only
+    when the compiler cannot build even a trivial function on this machine."""
+    if not _inductor_usable():
+        pytest.skip("torch.compile cannot build a trivial function here (compiler toolchain missing)")
+    import torch._dynamo
+    torch._dynamo.reset()
     g = load_golden("model_ref.npz")
     model = _model(g)
     ids = g["ids"].cuda()
-    try:
-        cmodel = torch.compile(model)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = cmodel(ids, ids)
-        loss.backward()
-    except Exception as e:  # compiler toolchain problems on the box are not this library's failure
-        if type(e).__module__.startswith("torch._inductor") or "libgomp" in str(e) or "gcc" in str(e).lower():
-            pytest.skip(f"inductor toolchain unavailable: {type(e).__name__}")
-        raise
+    cmodel = torch.compile(model, fullgraph=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = cmodel(ids, ids)
+    loss.backward()
     assert abs(float(loss) - float(g["loss_dezero"])) <= TOL * float(g["loss_dezero"])
+    for k, p in model.named_parameters():
+        assert rel_l2(p.grad.cpu(), g["grad/" + k]) <= TOL, k
 
 
 @pytest.mark.parametrize("bf16_weights", [False, True])

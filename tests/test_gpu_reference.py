@@ -68,7 +68,7 @@ def test_reference_model_runs_on_the_cuda_kernels_after_install(autocast):
         for k, p in model.named_parameters():
             ref = g["grad/" + k]
             err = rel_l2(p.grad.float().cpu(), ref)
-            assert err <= (3 * TOL if autocast else TOL), (k, err)
+            assert err <= (TOL if autocast else 5e-3), (k, err)
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
             logits = model(ids)
         assert rel_l2(logits.float().cpu(), g["logits_dezero"]) <= TOL
