@@ -270,6 +270,34 @@ __device__ __forceinline__ void gelu_pair_fast(float2 a, float2& phi, float2& g)
   phi.y = rcp_approx(d.y);
   g = mul2(a, phi);
 }
+// The same Phi with ONE transcendental: 1 / (1 + exp(-z)) = 0.5 + 0.5 tanh(z / 2), z = a q(a^2); the
+// coefficients are those of q times -ln(2)/2 relative to the table above, i.e. of q(s) / 2.  tanh.approx on
+// this part is accurate to 4e-6 ABSOLUTE over the whole range (measured; far inside its documented 2^-11
+// relative bound near saturation), so |gelu error| <= 4e-6 |a|: invisible norm-wise, but not "one bf16
+// rounding step" pointwise in the far negative tail, where gelu itself is below 1e-5.  Used by the scan
+// kernels' fused epilogue, which are MUFU-bound; the stand-alone gelu(a) * b kernels keep the 2-MUFU form.
+__device__ __forceinline__ void gelu_pair_tanh(float2 a, float2& phi, float2& g) {
+  const float2 s = mul2(a, a);
+  float2 q = fma2(s, f2(1.8056474e-09f), f2(-1.3344780e-07f));
+  q = fma2(q, s, f2(3.9691320e-06f));
+  q = fma2(q, s, f2(-5.5240323e-05f));
+  q = fma2(q, s, f2(-3.3129446e-05f));
+  q = fma2(q, s, f2(3.6334283e-02f));
+  q = fma2(q, s, f2(7.9788421e-01f));
+  float2 t = mul2(a, q);
+  t.x = tanh_approx(t.x);
+  t.y = tanh_approx(t.y);
+  phi = fma2(t, f2(0.5f), f2(0.5f));
+  g = mul2(a, phi);
+}
+__device__ __forceinline__ void gelu_pair_tanh_grad(float2 a, float2& g, float2& dg) {
+  float2 phi;
+  gelu_pair_tanh(a, phi, g);
+  float2 p = mul2(mul2(a, a), f2(-0.72134752044448171f));  // -log2(e) / 2
+  p.x = ex2_approx(p.x);
+  p.y = ex2_approx(p.y);
+  dg = fma2(mul2(a, f2(0.3989422804014327f)), p, phi);
+}
 // and the derivative Phi(a) + a pdf(a), pdf(a) = exp(-a^2 / 2) / sqrt(2 pi)
 __device__ __forceinline__ void gelu_pair_fast_grad(float2 a, float2& g, float2& dg) {
   float2 phi;

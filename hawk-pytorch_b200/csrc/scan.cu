@@ -63,13 +63,13 @@ struct SmemPair<__nv_bfloat16> {
   }
 };
 
-// gelu(y) and its derivative for the lane's channel pair: logistic form on the bf16 path (two / three MUFU
-// operations per element), erff for fp32 storage
+// gelu(y) and its derivative for the lane's channel pair: tanh form of the logistic GELU on the bf16 path
+// (one / two MUFU operations per element), erff for fp32 storage
 template <bool FAST>
 __device__ __forceinline__ float2 gelu2(float2 y) {
   if (FAST) {
     float2 phi, g;
-    gelu_pair_fast(y, phi, g);
+    gelu_pair_tanh(y, phi, g);
     return g;
   }
   return make_float2(gelu_f(y.x), gelu_f(y.y));
@@ -77,7 +77,7 @@ __device__ __forceinline__ float2 gelu2(float2 y) {
 template <bool FAST>
 __device__ __forceinline__ void gelu2_grad(float2 y, float2& g, float2& dg) {
   if (FAST) {
-    gelu_pair_fast_grad(y, g, dg);
+    gelu_pair_tanh_grad(y, g, dg);
   } else {
     gelu_and_grad(y.x, g.x, dg.x);
     gelu_and_grad(y.y, g.y, dg.y);
