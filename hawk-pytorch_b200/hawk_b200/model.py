@@ -126,12 +126,20 @@ class RNNCache:
 
 class Linear(nn.Linear):
     """nn.Linear without bias (same parameter name and state-dict key) whose forward goes through
-    `ops.linear`: under CUDA bf16 autocast the weight cast and the weight-gradient cast are fused away."""
+    `ops.linear`: under CUDA bf16 autocast the weight cast and the weight-gradient cast are fused away.
+
+    The bf16 copy an optimiser leaves here is trusted while `weight._version` is the version it was written
+    for.  Every in-place operation on the parameter, `load_state_dict` and `.to()` change the version (or the
+    tensor) and so fall back to a fresh cast; a write through `weight.data` (e.g. `weight.data.copy_(w)`) does
+    NOT change the version: after such a write call `drop_bf16_copy()` (or `drop_bf16_copies(model)`)."""
 
     # bf16 copy of the weight kept current by an optimiser that updates both in one pass
     # (train.FusedAdamW); valid only while the fp32 weight still has the version it was written for
     weight_bf16: Optional[torch.Tensor] = None
     weight_bf16_version: int = -1
+
+    def drop_bf16_copy(self) -> None:
+        self.weight_bf16, self.weight_bf16_version = None, -1
 
     def forward(self, x):
         if self.bias is not None:
@@ -141,6 +149,14 @@ class Linear(nn.Linear):
                                or wb.device != self.weight.device):
             wb = None  # stale, or traced code (which must not depend on a tensor's version): cast instead
         return ops.linear(x, self.weight, wb)
+
+
+def drop_bf16_copies(module: nn.Module) -> None:
+    """Forget the optimiser-written bf16 weight copies of every `Linear` under `module` (needed only after
+    writing weights behind autograd's back, see `Linear`)."""
+    for m in module.modules():
+        if isinstance(m, Linear):
+            m.drop_bf16_copy()
 
 
 class MLP(nn.Module):

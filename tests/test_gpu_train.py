@@ -78,3 +78,12 @@ def test_trainer_keeps_bf16_weight_copies_current():
         y = m(x)
         want = torch.nn.functional.linear(x, m.weight)
     assert torch.equal(y, want)
+    # a write through .data is invisible to the version counter: the documented remedy is drop_bf16_copies
+    tr.step(ids)
+    with torch.no_grad():
+        m.weight.data.mul_(2.0)
+    assert m.weight_bf16_version == m.weight._version  # the stale copy would be used ...
+    M.drop_bf16_copies(tr.model)
+    assert m.weight_bf16 is None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        assert torch.equal(m(x), torch.nn.functional.linear(x, m.weight))  # ... not after dropping it
