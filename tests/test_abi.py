@@ -129,3 +129,34 @@ def test_decode_block_step_argument_validation_needs_no_gpu():
     assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 256, 4, *ok_tail) == -7   # block wider than 128
     assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 128, 5, *ok_tail) == -7   # conv width
     assert lib.hawk_decode_block_step(p, 4096, *ptrs, 2, 2048, 128, 4, 1, 1, 9, None) == -3
+
+
+def test_fused_scan_and_gate_projection_argument_validation_needs_no_gpu():
+    lib = L.load()
+    p = ctypes.c_void_p(4096)
+    bf = L.HAWK_BF16
+    # x gx ga lam | gate_bias | y, y strides | h out
+    assert lib.hawk_scan_gelu_fwd(p, p, p, p, None, None, 8192, 128, p, p, 1, 8, 64, bf, None) == -1     # y missing
+    assert lib.hawk_scan_gelu_fwd(p, p, p, p, None, p, 8192, 32, p, p, 1, 8, 64, bf, None) == -2         # row stride < D
+    assert lib.hawk_scan_gelu_fwd(p, p, p, p, None, p, 8192, 132, p, p, 1, 8, 64, bf, None) == -4        # stride % 8
+    assert lib.hawk_scan_gelu_fwd(p, p, p, p, None, ctypes.c_void_p(4100), 8192, 128, p, p, 1, 8, 64, bf, None) == -4
+    assert lib.hawk_scan_gelu_fwd(p, p, p, p, None, p, 8192, 128, p, p, 1, 8, 96, bf, None) == -2        # D % 64
+    # x gx ga lam gate_bias h | y, strides | dout dx dgx dga | dy, strides | dlam dgate_bias | workspace
+    tail = (1, 8, 64, bf, None)
+    assert lib.hawk_scan_gelu_bwd(p, p, p, p, None, p, p, 8192, 128, p, p, p, p, None, 8192, 128, p, None, p, 256, *tail) == -1
+    assert lib.hawk_scan_gelu_bwd(p, p, p, p, None, p, p, 8192, 128, p, p, p, p, p, 8192, 128, p, None, p, 16, *tail) == -5
+    assert lib.hawk_scan_gelu_bwd(p, p, p, p, p, p, p, 8192, 128, p, p, p, p, p, 8192, 128, p, p, p, 256, *tail) == -5  # 3 planes
+    # gate projections: width a multiple of 128, block width dividing 128
+    assert lib.hawk_gates_packed_bytes(2048, 128) == 16 * (256 * 128 + 128 * 384) * 2
+    assert lib.hawk_gates_packed_bytes(2048, 96) == 0 and lib.hawk_gates_packed_bytes(192, 64) == 0
+    assert lib.hawk_gates_pack_weights(p, p, 0, p, 2048, 48, None) == -2
+    assert lib.hawk_gates_pack_weights(p, None, 0, p, 2048, 128, None) == -1
+    assert lib.hawk_gates_pack_weights(p, p, 5, p, 2048, 128, None) == -3
+    assert lib.hawk_gates_fwd(p, p, p, p, 4096, 2048, 128, None, None) == -1        # status word missing
+    assert lib.hawk_gates_fwd(p, p, p, p, 4096, 1000, 8, p, None) == -2
+    assert lib.hawk_gates_fwd(ctypes.c_void_p(4104), p, p, p, 4096, 2048, 128, p, None) == -4
+    need = lib.hawk_gates_bwd_workspace_bytes(4096, 2048, 128)
+    assert need >= 16 * 128 * 256 * 4
+    assert lib.hawk_gates_bwd(p, p, p, p, p, p, p, p, need - 1, 4096, 2048, 128, p, None) == -5
+    assert lib.hawk_debug_wait_timeout(p, 1024, 100000, p, None) == -5               # scratch too small
+    assert lib.hawk_debug_wait_timeout(p, 1 << 20, 10, p, None) == -2                # budget out of range
