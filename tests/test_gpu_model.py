@@ -89,10 +89,11 @@ def test_block_intermediates_with_injected_gradient():
     taps = {}
     ref = omodel.hawk_block(sdg, "b.", xs, taps=taps)
     ref.backward(go)
+    # measured on B200: output 4.5e-3, input gradient 5.2e-3, worst parameter gradient 6.1e-3 (conv1d.w)
     assert rel_l2(out.float().cpu(), ref.detach()) <= TOL
-    assert rel_l2(xd.grad.cpu(), xs.grad) <= 2 * TOL
+    assert rel_l2(xd.grad.cpu(), xs.grad) <= TOL
     for k, p in blk.named_parameters():
-        assert rel_l2(p.grad.cpu(), sdg["b." + k].grad) <= 3 * TOL, k
+        assert rel_l2(p.grad.cpu(), sdg["b." + k].grad) <= TOL, k
 
 
 def test_optimiser_trajectory_matches_oracle():
@@ -260,10 +261,11 @@ def test_config1_block_shape_matches_oracle():
     taps = {}
     ref = omodel.hawk_block(sdg, "b.", xs, taps=taps)
     ref.backward(go)
+    # measured on B200: output 4.5e-3, input gradient 5.2e-3, worst parameter gradient 6.1e-3 (conv1d.w)
     assert rel_l2(out.float().cpu(), ref.detach()) <= TOL
-    assert rel_l2(xd.grad.cpu(), xs.grad) <= 2 * TOL
+    assert rel_l2(xd.grad.cpu(), xs.grad) <= TOL
     for k, p in blk.named_parameters():
-        assert rel_l2(p.grad.cpu(), sdg["b." + k].grad) <= 3 * TOL, k
+        assert rel_l2(p.grad.cpu(), sdg["b." + k].grad) <= TOL, k
 
 
 def test_config2_readme_model_step():

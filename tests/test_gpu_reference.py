@@ -206,4 +206,4 @@ def test_untouched_reference_model_against_this_librarys_model():
     theirs_grads = dict(theirs.named_parameters())
     for k, p in ours.named_parameters():
         err = rel_l2(p.grad.float().cpu(), theirs_grads[k].grad.float().cpu())
-        assert err <= 3 * TOL, (k, err)
+        assert err <= 1.5 * TOL, (k, err)  # two bf16 computations against each other: measured worst 1.8e-2
