@@ -175,16 +175,20 @@ class Trainer:
     cross-entropy with labels = inputs), backward, gradient all-reduce and the optimiser update.
     `grad_comm_dtype`: torch.float32 (default: the gradients are all-reduced as they are) or torch.bfloat16
     (each bucket is rounded to bf16 for the all-reduce and restored: half the NVLink bytes).
-    `timeline`: a CommTimeline that the step fills (multi-GPU only)."""
+    `timeline`: a CommTimeline that the step fills (multi-GPU only).  `check_status_every`: see below."""
 
     def __init__(self, config: HawkConfig, device, seed: int = 0, lr: float = 3e-4, world_size: int = 1,
                  autocast: bool = True, bucket_cap_mb: int = 256, grad_comm_dtype: torch.dtype = torch.float32,
-                 timeline: Optional[CommTimeline] = None):
+                 timeline: Optional[CommTimeline] = None, check_status_every: int = 100):
         torch.manual_seed(seed)  # same seed on every rank: identical replicas
         self.device = torch.device(device)
         self.model = HawkModel(config).to(self.device)
         self.autocast = autocast and self.device.type == "cuda"
         self.ddp = None
+        self.steps_done = 0
+        # every this many steps the device status word of the tensor-core kernels is read back (one host sync):
+        # a kernel that gave up a bounded wait then raises here instead of training on (its loss is NaN anyway)
+        self.check_status_every = check_status_every
         self.timeline = timeline if world_size > 1 else None
         if world_size > 1:
             from torch.nn.parallel import DistributedDataParallel as DDP
@@ -214,4 +218,8 @@ class Trainer:
             after_backward(loss.detach())
         self.opt.step()
         self.opt.zero_grad(set_to_none=True)
+        self.steps_done += 1
+        if self.check_status_every > 0 and self.steps_done % self.check_status_every == 0 and self.device.type == "cuda":
+            from . import ops
+            ops.check_device_status(self.device)
         return loss.detach()
