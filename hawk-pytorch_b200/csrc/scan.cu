@@ -765,8 +765,12 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
 // with CW = 64 and 8 rows per slot when there are at least ~200 (batch x 64-channel group) pairs, else
 // with CW = 32 to double the CTA count.  (512-thread CTAs measured slower in both directions; backward
 // shapes with 4 rows per slot at 3 CTAs per SM, 78 registers, measured 264-266 us inside the step against
-// 254 us for the 8-row shape at 2 CTAs per SM.)  The fused-epilogue kernels stage one more input, so
-// their forward shapes hold one CTA fewer per SM (shared memory) or two stages instead of four.
+// 254 us for the 8-row shape at 2 CTAs per SM.)  With few groups the backward runs CW = 32 with 8 rows per
+// slot (B1 T65536 D4096: 0.960 against 1.038 ms for 4 rows and 4 stages).  The fused-epilogue kernels carry
+// more arithmetic per byte and come out best with CW = 32 in both directions where CW = 16 wins for the
+// plain forward: inside the training step 186 against 224 us forward (CW = 32 x 8 rows, 105 registers,
+// 4 CTAs per SM, against CW = 16 at 6 CTAs per SM), 0.750 against 0.914 ms at B1 T65536 D4096; eight other
+// forward shapes and eight backward shapes measured slower inside the step.
 static bool many_groups(int B, int D) { return (int64_t)B * (D / 64) >= 200; }
 
 static int check_scan_common(int B, int T, int D, int dtype) {
@@ -796,8 +800,8 @@ static int scan_fwd_dispatch(const void* x, const void* gx, const void* ga, cons
   const bool many = many_groups(B, D);
   if (dtype == HAWK_BF16) {
     if (ge) {
-      if (many) HAWK_FWD(bf, 8, 4, 8, 2, 6, true, true);
-      HAWK_FWD(bf, 8, 8, 8, 2, 3, true, true);
+      if (many) HAWK_FWD(bf, 8, 4, 16, 2, 4, true, true);
+      HAWK_FWD(bf, 8, 8, 16, 2, 2, true, true);
     }
     if (many) HAWK_FWD(bf, 8, 4, 8, 2, 7, true, false);
     HAWK_FWD(bf, 8, 8, 8, 4, 2, true, false);
@@ -820,10 +824,10 @@ static int scan_bwd_dispatch(const void* x, const void* gx, const void* ga, cons
   if (dtype == HAWK_BF16) {
     if (ge) {
       if (many) HAWK_BWD(bf, 8, 8, 32, 2, 2, true, true);
-      HAWK_BWD(bf, 4, 8, 16, 4, 2, true, true);
+      HAWK_BWD(bf, 8, 8, 16, 2, 2, true, true);
     }
     if (many) HAWK_BWD(bf, 8, 8, 32, 2, 2, true, false);
-    HAWK_BWD(bf, 4, 8, 16, 4, 2, true, false);
+    HAWK_BWD(bf, 8, 8, 16, 2, 2, true, false);
   }
   if (ge) {
     if (many) HAWK_BWD(float, 2, 8, 32, 4, 2, false, true);
