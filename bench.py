@@ -59,9 +59,9 @@ WORKLOAD = f"hawk_1b_train_step: {MODEL}; per-GPU B=8, T=4096; bf16 autocast, fu
 # launch at B=8, T=4096, D=2048 bf16 from one ncu capture of those two kernels: forward 405.2 + 110.5 MB,
 # backward 671.1 + 364.9 MB (part of the output is still in L2 when the kernel ends)
 SCAN_TRAFFIC_BYTES = 515_724_288 + 1_036_071_168
-# the same for the fused entry points (scan + gelu(y)*h), one ncu capture at the same shape: forward 550.0 +
-# 243.5 MB (algorithmic 536.9 + 268.4), backward 805.5 + 495.5 MB (algorithmic 805.3 + 536.9)
-FUSED_SCAN_TRAFFIC_BYTES = 549_962_240 + 243_548_160 + 805_502_464 + 495_513_088
+# the same for the fused entry points (scan + gelu(y)*h), one ncu capture at the same shape: forward 537.0 +
+# 239.7 MB (algorithmic 536.9 + 268.4), backward 805.4 + 496.5 MB (algorithmic 805.3 + 536.9)
+FUSED_SCAN_TRAFFIC_BYTES = 537_012_224 + 239_708_160 + 805_390_336 + 496_506_880
 
 
 def measured_peaks():

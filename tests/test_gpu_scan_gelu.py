@@ -76,8 +76,9 @@ def test_fused_scan_gelu_matches_oracle(B, T, D, dtype, tol):
 
 
 def test_fused_equals_separate_kernels_bf16():
-    """Same tensors through the fused kernels and through scan + gelu_mul: h bit-identical (the recurrence is
-    the same code), out / gradients within one bf16 rounding of each other."""
+    """Same tensors through the fused kernels and through scan + gelu_mul: h, out and the gradients within bf16
+    rounding of each other (the two paths use different launch shapes, so the fp32 recurrence is associated
+    differently and h may differ in the last bf16 bit)."""
     from hawk_b200 import fused_linear_scan, fused_scan_gelu, ops
     B, T, D = 8, 1024, 2048
     x, gx, ga, dout, xy, gb, lam = _inputs(B, T, D, seed=5, dtype=torch.bfloat16)
@@ -93,7 +94,7 @@ def test_fused_equals_separate_kernels_bf16():
     h2 = fused_linear_scan(*xs2, lam2, gate_bias=gb2)
     out2 = ops.gelu_mul(xyd2[..., D:], h2)
     out2.backward(dout.to(dev, dt))
-    assert torch.equal(h, h2)
+    assert rel_l2(h.float(), h2.float()) <= 2e-3
     assert rel_l2(out.float(), out2.float()) <= 4e-3
     for a, b in zip(xs + [xyd, lam_d, gb_d], xs2 + [xyd2, lam2, gb2]):
         assert rel_l2(a.grad.float(), b.grad.float()) <= 8e-3
