@@ -168,7 +168,7 @@ gates_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int tile = tile0; tile < m_tiles; tile += tstride, ++it) {
       const int acc = it & 1;
       // one thread waits for the accumulator (and for the previous stores to have read the staging buffer);
-      // the four warps take its verdict together, so none can be left behind at a barrier
+      // the four warps take its answer together, so none can be left behind at a barrier
       if (threadIdx.x == EPI_LEADER) {
         epi_ok = mbar_wait(&bars.tfull[acc], (it >> 1) & 1, abortp, wait_budget) ? 1 : 0;
         bulk_wait_read();
@@ -272,7 +272,7 @@ gates_dx_kernel(const __grid_constant__ CUtensorMap map_dgx, const __grid_consta
     for (int tile = tile0; tile < m_tiles; tile += tstride, ++it) {
       const int acc = it & 1;
       // one thread waits for the accumulator (and for the previous stores to have read the staging buffer);
-      // the four warps take its verdict together, so none can be left behind at a barrier
+      // the four warps take its answer together, so none can be left behind at a barrier
       if (threadIdx.x == EPI_LEADER) {
         epi_ok = mbar_wait(&bars.tfull[acc], (it >> 1) & 1, abortp) ? 1 : 0;
         bulk_wait_read();

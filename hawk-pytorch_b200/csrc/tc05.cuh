@@ -51,7 +51,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return true;
 }
-// The same for a whole warp: lane 0 waits, every lane takes its verdict, so the warp never diverges
+// The same for a whole warp: lane 0 waits, every lane takes its answer, so the warp never diverges
 // around the warp-wide tcgen05.ld that follows.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                long long budget = kWaitBudget) {
