@@ -292,3 +292,27 @@ def test_config2_readme_model_step():
     losses = [float(tr.step(ids)) for _ in range(4)]
     check_device_status()
     assert losses[0] == pytest.approx(math.log(32000), abs=1e-4) and min(losses[1:]) < losses[0] - 0.05, losses
+
+
+def test_config3_first_step_at_reference_init():
+    """Benchmark configuration 3 at full size (1.35 B parameters, B=8, T=4096, bf16 autocast): at the reference
+    init lm_head and every resid_proj are zero (hawk/hawk.py:79,128,258), so the first loss is ln(32000) and
+    lm_head.weight is the only parameter with a gradient: the one parity statement that is exact at this size."""
+    import hawk_b200.model as M
+    from hawk_b200 import check_device_status
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = M.HawkModel(M.hawk_1b_config())
+    assert sum(p.numel() for p in model.parameters()) == 1_352_108_032
+    ids = torch.randint(1, 32000, (8, 4096), generator=torch.Generator().manual_seed(0)).cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = model(ids, ids)
+    loss.backward()
+    check_device_status()
+    assert abs(float(loss) - math.log(32000)) <= 1e-4
+    for k, p in model.named_parameters():
+        if k != "lm_head.weight":
+            assert not bool((p.grad != 0).any()), k
+    gw = model.lm_head.weight.grad
+    assert torch.isfinite(gw).all() and float(gw.norm()) > 0
+    assert float(gw.sum(0).abs().max()) <= 2e-2 * float(gw.abs().sum(0).max())  # rows of softmax - onehot sum to zero
