@@ -458,7 +458,9 @@ def run_ours(args):
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     timeline = train.CommTimeline() if world > 1 else None
-    trainer = train.Trainer(M.hawk_1b_config(), dev, seed=0, world_size=world, timeline=timeline)
+    trainer = train.Trainer(M.hawk_1b_config(), dev, seed=0, world_size=world, timeline=timeline,
+                            bucket_cap_mb=args.bucket_mb,
+                            grad_comm_dtype=torch.bfloat16 if args.grad_comm_dtype == "bf16" else torch.float32)
     g = torch.Generator().manual_seed(1234 + rank)
     n_host = warmup + steps
     host_ids = torch.randint(1, VOCAB, (n_host, B_PER_GPU, SEQ_LEN), generator=g).pin_memory()
@@ -605,6 +607,8 @@ def run_ours(args):
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / steps, "last_loss": last},
         "gpu_launches": launches, "roofline": roofline, "kernels": kernels, "clocks": clocks, "parity": parity,
     }
+    if world > 1:
+        line["config"]["grad_all_reduce"] = {"dtype": args.grad_comm_dtype, "bucket_mb": args.bucket_mb}
     if comm is not None:
         comm["what"] = ("gradient all-reduce per DDP bucket in one step on rank 0: time from the bucket being ready on the "
                         "compute stream to its all-reduce being done, and how far the last all-reduce ran past the moment "
@@ -639,6 +643,10 @@ def main():
                     help="skip the CPU-oracle leg (e.g. when the command runs under a profiler)")
     ap.add_argument("--no-configs", action="store_true", help="skip the other configurations (N = 1 only)")
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip the reference-on-GPU block (N = 1 only)")
+    ap.add_argument("--grad-comm-dtype", default="f32", choices=["f32", "bf16"],
+                    help="N > 1: dtype of the gradient all-reduce (bf16 halves the NVLink bytes)")
+    ap.add_argument("--bucket-mb", type=int, default=256,
+                    help="N > 1: DDP bucket size; larger than the 5.4 GB of gradients = one all-reduce after the backward")
     ap.add_argument("--reference-gpu-compile", action="store_true",
                     help="also time the reference training step with torch.compile(model) (minutes of compilation)")
     args = ap.parse_args()

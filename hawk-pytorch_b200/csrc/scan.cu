@@ -276,12 +276,16 @@ struct Geo {
 // forward
 // ----------------------------------------------------------------------------------------------
 // GELU: y is the [B,T,D] view with strides (y_bs, y_ld) elements; out = gelu(y) * h is [B,T,D] contiguous.
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
+// SUMMARY (time-split scans): no stores of h; instead the CTA writes, per channel, the product of its
+// sequence's decays and its end state from a zero start -- the affine map h_in -> h_end = P * h_in + h_loc of
+// the whole (sub)sequence -- into sum_P / sum_h [B, D].
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU, bool SUMMARY = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
                 const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
                 T* __restrict__ h, int T_len, int D, const T* __restrict__ y, size_t y_bs, uint32_t y_ld,
-                T* __restrict__ out) {
+                T* __restrict__ out, float* __restrict__ sum_P = nullptr, float* __restrict__ sum_h = nullptr) {
+  static_assert(!(SUMMARY && GELU), "the summary pass does not touch y");
   using G = Geo<T, R, WARPS, LPR, GELU ? 4 : 3>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -357,6 +361,7 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 
   T* hp = h + base + ch;
   T* outp = GELU ? out + base + ch : nullptr;
+  float2 Ptot = f2(1.f), hend = f2(0.f);  // SUMMARY: the last slot's running product and end state
   // One super-step.  FULL = every row is inside the sequence: no per-row predicates.
   auto step = [&](int s, auto full_tag) {
     constexpr bool FULL = decltype(full_tag)::value;
@@ -392,11 +397,18 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P.x, P.y, hl.x, hl.y);
     __syncthreads();
     float2 hin = state[s & 1][cl];
+    float2 Pin = f2(1.f);
     for (int j = 0; j < warp; ++j) {
       const float4 c = carry[s & 1][j][cl];
       hin = fma2(make_float2(c.x, c.y), hin, make_float2(c.z, c.w));
+      if (SUMMARY) Pin = mul2(Pin, make_float2(c.x, c.y));
     }
-    if (slot == G::SLOTS - 1) state[(s + 1) & 1][cl] = fma2(P, hin, hl);
+    if (slot == G::SLOTS - 1) {
+      hend = fma2(P, hin, hl);
+      state[(s + 1) & 1][cl] = hend;
+      if (SUMMARY) Ptot = mul2(Ptot, mul2(P, Pin));
+    }
+    if (SUMMARY) return;
     hin = fma2(eP, hin, eh);
 
     // phase 3: replay from the true inbound state and store
@@ -422,20 +434,31 @@ scan_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   for (int s = 0; s < nfull; ++s) step(s, std::true_type{});
   if (nfull < nsteps) step(nfull, std::false_type{});
   cp_async_wait<0>();
+  if (SUMMARY && slot == G::SLOTS - 1) {
+    *reinterpret_cast<float2*>(sum_P + (size_t)b * D + ch) = Ptot;
+    *reinterpret_cast<float2*>(sum_h + (size_t)b * D + ch) = hend;
+  }
 }
 
 // ----------------------------------------------------------------------------------------------
 // backward
 // ----------------------------------------------------------------------------------------------
 // GELU: `go` is d out; y and dy are [B,T,D] views with strides (y_bs, y_ld) / (dy_bs, dy_ld) elements.
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
+// Time-split scans launch this kernel over sub-sequences (batch row b = sequence * nsub + chunk): `cin`
+// [B, D] is then the adjoint state arriving from the sub-sequence after this one (null: zero), h0 the state
+// before its first row, and only a sequence's first chunk writes dh0 [B / nsub, D].  SUMMARY: no gradient
+// stores; the CTA writes the affine map c_in -> c_out = P * c_in + c_loc of its sub-sequence's adjoint
+// recurrence into sum_P / sum_c [B, D] (only ga, d out and y are staged).
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU, bool SUMMARY = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __restrict__ ga,
                 const float* __restrict__ lam, const float* __restrict__ h0, const float* __restrict__ gbias,
                 const T* __restrict__ h, const T* __restrict__ go, T* __restrict__ dx, T* __restrict__ dgx,
                 T* __restrict__ dga, float* __restrict__ dlam_partial, float* __restrict__ dgb_partial,
                 float* __restrict__ dh0, int T_len, int D, int B_total, const T* __restrict__ y, size_t y_bs,
-                uint32_t y_ld, T* __restrict__ dy, size_t dy_bs, uint32_t dy_ld) {
+                uint32_t y_ld, T* __restrict__ dy, size_t dy_bs, uint32_t dy_ld,
+                const float* __restrict__ cin = nullptr, int nsub = 1, float* __restrict__ sum_P = nullptr,
+                float* __restrict__ sum_c = nullptr) {
   using G = Geo<T, R, WARPS, LPR, GELU ? 6 : 5>;
   using P_ = Pair<T>;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -464,7 +487,10 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   uint32_t fgx, fga;
   exp_gate_terms(gbias, 0, D, ch, egx, fgx);
   exp_gate_terms(gbias, 1, D, ch, ega, fga);
-  if (threadIdx.x < LPR) state[0][threadIdx.x] = make_float2(0.f, 0.f);  // c_T = 0
+  if (threadIdx.x < LPR) {  // c_T = 0, or what the following sub-sequence hands back
+    state[0][threadIdx.x] = cin ? *reinterpret_cast<const float2*>(cin + (size_t)b * D + ch0 + 2 * threadIdx.x)
+                                : make_float2(0.f, 0.f);
+  }
 
   static_assert((STAGES & (STAGES - 1)) == 0, "STAGES must be a power of two");
   unsigned char* ring = smem + (size_t)warp * STAGES * G::STAGE_BYTES;
@@ -500,8 +526,8 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
           const uint32_t o = (uint32_t)t * uD + cp_col;
           const uint32_t d = dst0 + c * G::RPI * G::ROWB;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) cp_async16(d + q * G::IN_BYTES, src[q] + o);
-          if (t > 0) cp_async16(d + 4 * G::IN_BYTES, src[4] + (o - uD));
+          for (int q = 0; q < (SUMMARY ? 2 : 4); ++q) cp_async16(d + q * G::IN_BYTES, src[q] + o);
+          if (!SUMMARY && t > 0) cp_async16(d + 4 * G::IN_BYTES, src[4] + (o - uD));
           if (GELU) cp_async16(d + 5 * G::IN_BYTES, ysrc + ((uint32_t)t * y_ld + cp_col));
         }
       }
@@ -512,6 +538,7 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
+  float2 Ptot = f2(1.f), cend = f2(0.f);  // SUMMARY: the last slot's running product and end state
   float2 acc = f2(0.f);  // sum over t of dlog_a * r  (times C*sigmoid(lam) at the end)
   float2 acc_bx = f2(0.f), acc_ba = f2(0.f);  // sums over t of d gx, d ga: the gate-bias gradients
   T* dxp = dx + base + ch;
@@ -543,13 +570,16 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
         if (GELU) {
           float2 g, dg;
           gelu2_grad<FAST>(SmemPair<T>::ld(row + 5 * G::IN_BYTES), g, dg);
-          SmemPair<T>::st(row + 5 * G::IN_BYTES, mul2(gov, dg));
+          if (!SUMMARY) SmemPair<T>::st(row + 5 * G::IN_BYTES, mul2(gov, dg));
           gov = SmemPair<T>::st(row + G::IN_BYTES, mul2(gov, g));
         }
+        // (SUMMARY stages no gx: the input gate, unused there, is computed from ga and dropped)
+        constexpr int GXQ = SUMMARY ? 0 : 3;
         if (FAST)
-          gates2_exp(ld_floored_bf16x2(row + 3 * G::IN_BYTES, fgx), ld_floored_bf16x2(row, fga), egx, ega, ig[r], rg[r]);
+          gates2_exp(ld_floored_bf16x2(row + GXQ * G::IN_BYTES, SUMMARY ? fga : fgx), ld_floored_bf16x2(row, fga), egx, ega,
+                     ig[r], rg[r]);
         else
-          gates2<FAST>(SmemPair<T>::ld(row + 3 * G::IN_BYTES), SmemPair<T>::ld(row), bgx, bga, ig[r], rg[r]);
+          gates2<FAST>(SmemPair<T>::ld(row + GXQ * G::IN_BYTES), SmemPair<T>::ld(row), bgx, bga, ig[r], rg[r]);
         a[r] = decay2<FAST>(k2, rg[r]);
       } else {
         rg[r] = ig[r] = f2(0.f);
@@ -565,11 +595,18 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     if (sub == G::NSUB - 1) carry[s & 1][warp][cl] = make_float4(P.x, P.y, cloc.x, cloc.y);
     __syncthreads();
     float2 c = state[s & 1][cl];
+    float2 Pin = f2(1.f);
     for (int j = 0; j < warp; ++j) {
       const float4 cj = carry[s & 1][j][cl];
       c = fma2(make_float2(cj.x, cj.y), c, make_float2(cj.z, cj.w));
+      if (SUMMARY) Pin = mul2(Pin, make_float2(cj.x, cj.y));
     }
-    if (slot == G::SLOTS - 1) state[(s + 1) & 1][cl] = fma2(P, c, cloc);
+    if (slot == G::SLOTS - 1) {
+      cend = fma2(P, c, cloc);
+      state[(s + 1) & 1][cl] = cend;
+      if (SUMMARY) Ptot = mul2(Ptot, mul2(P, Pin));
+    }
+    if (SUMMARY) return;
     c = fma2(eP, c, eh);
 
     // phase 3: dh_t and everything that is linear in it
@@ -652,6 +689,13 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
   for (int s = 0; s < nfast; ++s) step(s, std::true_type{});
   for (int s = nfast; s < nsteps; ++s) step(s, std::false_type{});
   cp_async_wait<0>();
+  if (SUMMARY) {
+    if (slot == G::SLOTS - 1) {
+      *reinterpret_cast<float2*>(sum_P + (size_t)b * D + ch) = Ptot;
+      *reinterpret_cast<float2*>(sum_c + (size_t)b * D + ch) = cend;
+    }
+    return;
+  }
 
   // d(lam) partial for this (batch row, channel pair): C * sigmoid(lam) * sum_t dlog_a * r
   red[slot][cl] = acc;
@@ -668,9 +712,9 @@ scan_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gx, const T* __re
     const float sl0 = 1.f / (1.f + expf(-l2.x)), sl1 = 1.f / (1.f + expf(-l2.y));  // softplus_bwd :23-25
     *reinterpret_cast<float2*>(dlam_partial + (size_t)b * D + ch0 + 2 * c2) =
         make_float2(kGateC * sl0 * s0, kGateC * sl1 * s1);
-    if (dh0) {
+    if (dh0 && b % nsub == 0) {
       // c_0 = a_0 * dh_0 = d h_{-1}
-      *reinterpret_cast<float2*>(dh0 + (size_t)b * D + ch0 + 2 * c2) = state[nsteps & 1][c2];
+      *reinterpret_cast<float2*>(dh0 + (size_t)(b / nsub) * D + ch0 + 2 * c2) = state[nsteps & 1][c2];
     }
   }
   if (dgb_partial != nullptr) {  // gate-bias gradient partials [2][B][D], same fixed-order reduction
@@ -705,6 +749,51 @@ __global__ void scan_dlam_reduce_kernel(const float* __restrict__ partial, float
   if (v == 0) dlam[d] = s; else dgb[(size_t)(v - 1) * D + d] = s;
 }
 
+// ---- time-split scans ---------------------------------------------------------------------------
+// A CTA walks all of T for its channel group, so a launch has B * D / CW CTAs: one long sequence of a narrow
+// model leaves most SMs idle.  The split cuts every sequence into nsub sub-sequences of T / nsub rows and runs
+// three launches: (1) SUMMARY kernels reduce each sub-sequence to its affine map state_in -> state_out,
+// (2) the kernel below composes the maps along each sequence (forward in time for h, backward for the adjoint)
+// into the state entering every sub-sequence, (3) the ordinary kernels run over the B * nsub sub-sequences
+// from those states.  Inputs are read twice; the CTA count grows by nsub.  (The reference walks T in one
+// warp per channel block: scan_fused.py:83.)
+//
+// inbound[b][c] = state entering sub-sequence c of sequence b; start [B, D] (null: zero) enters the first one
+// in walking order.
+__global__ void __launch_bounds__(256)
+scan_split_compose_kernel(const float* __restrict__ sum_P, const float* __restrict__ sum_s,
+                          const float* __restrict__ start, float* __restrict__ inbound, int B, int nsub, int D,
+                          int reverse) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)B * D) return;
+  const int b = (int)(i / D), d = (int)(i - (int64_t)b * D);
+  float s = start ? start[i] : 0.f;
+  for (int k = 0; k < nsub; ++k) {
+    const int c = reverse ? nsub - 1 - k : k;
+    const size_t o = ((size_t)b * nsub + c) * D + d;
+    inbound[o] = s;
+    s = fmaf(sum_P[o], s, sum_s[o]);
+  }
+}
+
+// hprev[b][c] = h of the row before sub-sequence c (stored precision, as the backward reads h_{t-1} elsewhere);
+// c = 0: h0 [B, D] or zero
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_split_hprev_kernel(const T* __restrict__ h, const float* __restrict__ h0, float* __restrict__ hprev, int B,
+                        int nsub, int L, int D) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)B * nsub * D) return;
+  const int d = (int)(i % D);
+  const int64_t bc = i / D;
+  const int c = (int)(bc % nsub);
+  const int64_t b = bc / nsub;
+  float v;
+  if (c == 0) v = h0 ? h0[b * D + d] : 0.f;
+  else v = to_float(h[(b * nsub * (int64_t)L + (int64_t)c * L - 1) * D + d]);
+  hprev[i] = v;
+}
+
 // ---- launch ---------------------------------------------------------------------------------
 struct GeluArgs {  // the fused gelu(y) * h epilogue: y / dy as [B,T,D] views (strides in elements), out contiguous
   const void* y = nullptr;
@@ -716,11 +805,20 @@ struct GeluArgs {  // the fused gelu(y) * h epilogue: y / dy as [B,T,D] views (s
   uint32_t dy_ld = 0;
 };
 
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
+// the extra arguments of a time-split scan (defaults: a whole-sequence scan)
+struct SplitArgs {
+  const float* cin = nullptr;  // backward: adjoint state entering each sub-sequence from the one after it
+  int nsub = 1;                // sub-sequences per sequence (backward: who writes dh0)
+  float* sum_P = nullptr;      // SUMMARY outputs [B, D]
+  float* sum_s = nullptr;
+};
+
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU, bool SUMMARY = false>
 static int launch_fwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
-                      const float* gbias, void* h, int B, int T_len, int D, const GeluArgs& ge, cudaStream_t st) {
+                      const float* gbias, void* h, int B, int T_len, int D, const GeluArgs& ge, cudaStream_t st,
+                      const SplitArgs& sp = SplitArgs()) {
   using G = Geo<T, R, WARPS, LPR, GELU ? 4 : 3>;
-  auto kern = scan_fwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU>;
+  auto kern = scan_fwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU, SUMMARY>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -729,17 +827,17 @@ static int launch_fwd(const void* x, const void* gx, const void* ga, const float
   kern<<<B * (D / G::CW), WARPS * 32, smem, st>>>(static_cast<const T*>(x), static_cast<const T*>(gx),
                                                    static_cast<const T*>(ga), lam, h0, gbias, static_cast<T*>(h),
                                                    T_len, D, static_cast<const T*>(ge.y), ge.y_bs, ge.y_ld,
-                                                   static_cast<T*>(ge.out));
+                                                   static_cast<T*>(ge.out), sp.sum_P, sp.sum_s);
   return launch_status();
 }
 
-template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU>
+template <typename T, int R, int WARPS, int LPR, int STAGES, int MINB, bool FAST, bool GELU, bool SUMMARY = false>
 static int launch_bwd(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
                       const float* gbias, const void* h, const void* go, void* dx, void* dgx, void* dga,
                       float* dlam, float* dh0, float* dgbias, float* partial, int B, int T_len, int D,
-                      const GeluArgs& ge, cudaStream_t st) {
+                      const GeluArgs& ge, cudaStream_t st, const SplitArgs& sp = SplitArgs()) {
   using G = Geo<T, R, WARPS, LPR, GELU ? 6 : 5>;
-  auto kern = scan_bwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU>;
+  auto kern = scan_bwd_kernel<T, R, WARPS, LPR, STAGES, MINB, FAST, GELU, SUMMARY>;
   constexpr int smem = WARPS * STAGES * G::STAGE_BYTES;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -749,9 +847,10 @@ static int launch_bwd(const void* x, const void* gx, const void* ga, const float
       static_cast<const T*>(x), static_cast<const T*>(gx), static_cast<const T*>(ga), lam, h0, gbias,
       static_cast<const T*>(h), static_cast<const T*>(go), static_cast<T*>(dx), static_cast<T*>(dgx),
       static_cast<T*>(dga), partial, dgbias ? partial + (size_t)B * D : nullptr, dh0, T_len, D, B,
-      static_cast<const T*>(ge.y), ge.y_bs, ge.y_ld, static_cast<T*>(ge.dy), ge.dy_bs, ge.dy_ld);
+      static_cast<const T*>(ge.y), ge.y_bs, ge.y_ld, static_cast<T*>(ge.dy), ge.dy_bs, ge.dy_ld, sp.cin, sp.nsub,
+      sp.sum_P, sp.sum_s);
   int rc = launch_status();
-  if (rc != HAWK_OK) return rc;
+  if (rc != HAWK_OK || SUMMARY) return rc;
   const int nvec = dgbias ? 3 : 1;
   scan_dlam_reduce_kernel<<<(nvec * D + 255) / 256, 256, 0, st>>>(partial, dlam, dgbias, B, D, nvec);
   return launch_status();
@@ -792,9 +891,16 @@ static int check_view(const void* p, int64_t bs, int64_t ld, int T, int D, int d
 
 static int scan_fwd_dispatch(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
                              const float* gate_bias, void* h, int B, int T, int D, int dtype, const GeluArgs* ge,
-                             cudaStream_t st) {
+                             cudaStream_t st, const SplitArgs* summary = nullptr) {
   using bf = __nv_bfloat16;
   const GeluArgs none;
+  if (summary) {  // one shape per storage type: the pass exists to raise the CTA count of small launches
+    if (dtype == HAWK_BF16)
+      return launch_fwd<bf, 8, 4, 16, 2, 4, true, false, true>(x, gx, ga, lam, nullptr, gate_bias, nullptr, B, T, D, none, st,
+                                                               *summary);
+    return launch_fwd<float, 4, 4, 8, 4, 4, false, false, true>(x, gx, ga, lam, nullptr, gate_bias, nullptr, B, T, D, none, st,
+                                                                *summary);
+  }
 #define HAWK_FWD(TT, R, W, LPR, S, MINB, FAST, GELU) \
   return launch_fwd<TT, R, W, LPR, S, MINB, FAST, GELU>(x, gx, ga, lam, h0, gate_bias, h, B, T, D, ge ? *ge : none, st)
   const bool many = many_groups(B, D);
@@ -814,12 +920,28 @@ static int scan_fwd_dispatch(const void* x, const void* gx, const void* ga, cons
 static int scan_bwd_dispatch(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
                              const float* gate_bias, const void* h, const void* go, void* dx, void* dgx, void* dga,
                              float* dlam, float* dh0, float* dgate_bias, float* partial, int B, int T, int D,
-                             int dtype, const GeluArgs* ge, cudaStream_t st) {
+                             int dtype, const GeluArgs* ge, cudaStream_t st, const SplitArgs* split = nullptr,
+                             bool summary = false) {
   using bf = __nv_bfloat16;
   const GeluArgs none;
+  const SplitArgs whole;
+  if (summary) {
+#define HAWK_BWD_SUM(TT, R, W, LPR, S, MINB, FAST, GELU)                                                              \
+  return launch_bwd<TT, R, W, LPR, S, MINB, FAST, GELU, true>(x, gx, ga, lam, nullptr, gate_bias, h, go, nullptr, nullptr, \
+                                                              nullptr, nullptr, nullptr, nullptr, nullptr, B, T, D,   \
+                                                              ge ? *ge : none, st, *split)
+    if (dtype == HAWK_BF16) {
+      if (ge) HAWK_BWD_SUM(bf, 8, 8, 16, 2, 2, true, true);
+      HAWK_BWD_SUM(bf, 8, 8, 16, 2, 2, true, false);
+    }
+    if (ge) HAWK_BWD_SUM(float, 2, 8, 16, 4, 2, false, true);
+    HAWK_BWD_SUM(float, 2, 8, 16, 4, 2, false, false);
+#undef HAWK_BWD_SUM
+  }
 #define HAWK_BWD(TT, R, W, LPR, S, MINB, FAST, GELU)                                                                  \
   return launch_bwd<TT, R, W, LPR, S, MINB, FAST, GELU>(x, gx, ga, lam, h0, gate_bias, h, go, dx, dgx, dga, dlam, dh0, \
-                                                        dgate_bias, partial, B, T, D, ge ? *ge : none, st)
+                                                        dgate_bias, partial, B, T, D, ge ? *ge : none, st,            \
+                                                        split ? *split : whole)
   const bool many = many_groups(B, D);
   if (dtype == HAWK_BF16) {
     if (ge) {
@@ -923,6 +1045,139 @@ extern "C" int hawk_scan_gelu_bwd(const void* x, const void* gx, const void* ga,
   ge.dy_ld = (uint32_t)dy_row_stride;
   return scan_bwd_dispatch(x, gx, ga, lam, nullptr, gate_bias, h, dout, dx, dgx, dga, dlam, nullptr, dgate_bias,
                            static_cast<float*>(workspace), B, T, D, dtype, &ge, static_cast<cudaStream_t>(stream));
+}
+
+// ---- time-split entry points -------------------------------------------------------------------
+namespace hawk {
+constexpr int kSplitMaxSub = 64;
+constexpr int kSplitMinRows = 256;
+constexpr int kSplitPlanes = 7;  // P, s, inbound, hprev + three planes of parameter-gradient partials
+
+static int check_split(int B, int T, int D, int nsub, int dtype) {
+  HAWK_REQUIRE(valid_dtype(dtype), HAWK_ERR_DTYPE);
+  HAWK_REQUIRE(B >= 1 && T >= 1 && nsub >= 1 && nsub <= kSplitMaxSub && T % nsub == 0, HAWK_ERR_SHAPE);
+  HAWK_REQUIRE((int64_t)B * nsub <= 0x7fffffffLL / 4096, HAWK_ERR_SHAPE);
+  return check_scan_common(B * nsub, T / nsub, D, dtype);
+}
+
+// y / dy of the sub-sequences as a [B * nsub, T / nsub, D] view: needs consecutive sequences T rows apart
+static int split_view(const void* p, int64_t bs, int64_t ld, int T, int L, int D, int dtype, size_t align, size_t* vbs,
+                      uint32_t* vld) {
+  int rc = check_view(p, bs, ld, L, D, dtype, align);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(bs == (int64_t)T * ld, HAWK_ERR_UNSUPPORTED);
+  *vbs = (size_t)L * (size_t)ld;
+  *vld = (uint32_t)ld;
+  return HAWK_OK;
+}
+}  // namespace hawk
+
+extern "C" int hawk_scan_split_chunks(int B, int T, int D) {
+  if (B < 1 || T < 1 || D < 64) return 1;
+  const int64_t ctas = (int64_t)B * (D / 32);  // of the whole-sequence launch at its widest shape
+  if (ctas > 64) return 1;                     // at least ~0.4 CTAs per SM already: reading twice costs more
+  const int want = (int)((2 * 148 + ctas - 1) / ctas);
+  for (int n = want; n <= kSplitMaxSub; ++n)
+    if (T % n == 0 && T / n >= kSplitMinRows) return n;
+  for (int n = want - 1; n >= 2; --n)
+    if (T % n == 0 && T / n >= kSplitMinRows) return n;
+  return 1;
+}
+
+extern "C" size_t hawk_scan_split_workspace_bytes(int B, int nsub, int D) {
+  if (B < 1 || nsub < 1 || D < 1) return 0;
+  return (size_t)kSplitPlanes * (size_t)B * (size_t)nsub * (size_t)D * sizeof(float);
+}
+
+extern "C" int hawk_scan_fwd_split(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                                   const float* gate_bias, const void* y, int64_t y_batch_stride,
+                                   int64_t y_row_stride, void* h, void* out, int nsub, void* workspace,
+                                   size_t workspace_bytes, int B, int T, int D, int dtype, void* stream) {
+  HAWK_REQUIRE(x && gx && ga && lam && h && ((y == nullptr) == (out == nullptr)), HAWK_ERR_NULL);
+  int rc = check_split(B, T, D, nsub, dtype);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(workspace && workspace_bytes >= hawk_scan_split_workspace_bytes(B, nsub, D), HAWK_ERR_WORKSPACE);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(out, 16) &&
+                   aligned(lam, 8) && aligned(h0, 8) && aligned(gate_bias, 8) && aligned(workspace, 16),
+               HAWK_ERR_ALIGN);
+  const int L = T / nsub, Bs = B * nsub;
+  GeluArgs ge;
+  if (y) {
+    rc = split_view(y, y_batch_stride, y_row_stride, T, L, D, dtype, 16, &ge.y_bs, &ge.y_ld);
+    if (rc != HAWK_OK) return rc;
+    ge.y = y;
+    ge.out = out;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t plane = (size_t)Bs * D;
+  float* ws = static_cast<float*>(workspace);
+  SplitArgs sum;
+  sum.sum_P = ws;
+  sum.sum_s = ws + plane;
+  float* inbound = ws + 2 * plane;
+  rc = scan_fwd_dispatch(x, gx, ga, lam, nullptr, gate_bias, nullptr, Bs, L, D, dtype, nullptr, st, &sum);
+  if (rc != HAWK_OK) return rc;
+  scan_split_compose_kernel<<<(unsigned)(((int64_t)B * D + 255) / 256), 256, 0, st>>>(sum.sum_P, sum.sum_s, h0, inbound, B,
+                                                                                    nsub, D, 0);
+  rc = launch_status();
+  if (rc != HAWK_OK) return rc;
+  return scan_fwd_dispatch(x, gx, ga, lam, inbound, gate_bias, h, Bs, L, D, dtype, y ? &ge : nullptr, st);
+}
+
+extern "C" int hawk_scan_bwd_split(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                                   const float* gate_bias, const void* h, const void* y, int64_t y_batch_stride,
+                                   int64_t y_row_stride, const void* go, void* dx, void* dgx, void* dga, void* dy,
+                                   int64_t dy_batch_stride, int64_t dy_row_stride, float* dlam, float* dh0,
+                                   float* dgate_bias, int nsub, void* workspace, size_t workspace_bytes, int B,
+                                   int T, int D, int dtype, void* stream) {
+  HAWK_REQUIRE(x && gx && ga && lam && h && go && dx && dgx && dga && dlam && ((y == nullptr) == (dy == nullptr)),
+               HAWK_ERR_NULL);
+  int rc = check_split(B, T, D, nsub, dtype);
+  if (rc != HAWK_OK) return rc;
+  HAWK_REQUIRE(workspace && workspace_bytes >= hawk_scan_split_workspace_bytes(B, nsub, D), HAWK_ERR_WORKSPACE);
+  HAWK_REQUIRE(aligned(x, 16) && aligned(gx, 16) && aligned(ga, 16) && aligned(h, 16) && aligned(go, 16) &&
+                   aligned(dx, 8) && aligned(dgx, 8) && aligned(dga, 8) && aligned(lam, 8) && aligned(h0, 8) &&
+                   aligned(dh0, 8) && aligned(gate_bias, 8) && aligned(dgate_bias, 4) && aligned(workspace, 16),
+               HAWK_ERR_ALIGN);
+  const int L = T / nsub, Bs = B * nsub;
+  GeluArgs ge;
+  if (y) {
+    rc = split_view(y, y_batch_stride, y_row_stride, T, L, D, dtype, 16, &ge.y_bs, &ge.y_ld);
+    if (rc != HAWK_OK) return rc;
+    rc = split_view(dy, dy_batch_stride, dy_row_stride, T, L, D, dtype, 8, &ge.dy_bs, &ge.dy_ld);
+    if (rc != HAWK_OK) return rc;
+    ge.y = y;
+    ge.dy = dy;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t plane = (size_t)Bs * D;
+  float* ws = static_cast<float*>(workspace);
+  SplitArgs sum;
+  sum.sum_P = ws;
+  sum.sum_s = ws + plane;
+  float* cin = ws + 2 * plane;
+  float* hprev = ws + 3 * plane;
+  float* partial = ws + 4 * plane;
+  const unsigned gather_grid = (unsigned)((plane + 255) / 256);
+  if (dtype == HAWK_BF16)
+    scan_split_hprev_kernel<__nv_bfloat16><<<gather_grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h), h0, hprev, B,
+                                                                       nsub, L, D);
+  else
+    scan_split_hprev_kernel<float><<<gather_grid, 256, 0, st>>>(static_cast<const float*>(h), h0, hprev, B, nsub, L, D);
+  rc = launch_status();
+  if (rc != HAWK_OK) return rc;
+  rc = scan_bwd_dispatch(x, gx, ga, lam, nullptr, gate_bias, h, go, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                         nullptr, Bs, L, D, dtype, y ? &ge : nullptr, st, &sum, true);
+  if (rc != HAWK_OK) return rc;
+  scan_split_compose_kernel<<<(unsigned)(((int64_t)B * D + 255) / 256), 256, 0, st>>>(sum.sum_P, sum.sum_s, nullptr, cin, B,
+                                                                                    nsub, D, 1);
+  rc = launch_status();
+  if (rc != HAWK_OK) return rc;
+  SplitArgs run;
+  run.cin = cin;
+  run.nsub = nsub;
+  return scan_bwd_dispatch(x, gx, ga, lam, hprev, gate_bias, h, go, dx, dgx, dga, dlam, dh0, dgate_bias, partial, Bs, L, D,
+                           dtype, y ? &ge : nullptr, st, &run);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libhawk_b200.so")
 
 HAWK_F32 = 0
 HAWK_BF16 = 1
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _P = c_void_p
 # name -> (restype, argtypes); mirrors include/hawk_b200.h one to one
@@ -28,6 +28,11 @@ SIGNATURES = {
     "hawk_scan_gelu_bwd": (c_int, [_P] * 7 + [c_int64, c_int64] + [_P] * 5 + [c_int64, c_int64, _P, _P, _P, c_size_t,
                                   c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_noalloc": (c_int, [_P] * 12 + [c_int, c_int, c_int, c_int, _P]),
+    "hawk_scan_split_chunks": (c_int, [c_int, c_int, c_int]),
+    "hawk_scan_split_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "hawk_scan_fwd_split": (c_int, [_P] * 7 + [c_int64, c_int64, _P, _P, c_int, _P, c_size_t, c_int, c_int, c_int, c_int, _P]),
+    "hawk_scan_bwd_split": (c_int, [_P] * 8 + [c_int64, c_int64] + [_P] * 5 + [c_int64, c_int64, _P, _P, _P, c_int, _P,
+                                   c_size_t, c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_fwd": (c_int, [_P, c_int64, c_int64, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "hawk_conv1d_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "hawk_conv1d_bwd": (c_int, [_P, _P, c_int64, c_int64, _P, _P, c_int64, c_int64, _P, _P, _P, c_size_t,

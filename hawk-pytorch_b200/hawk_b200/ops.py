@@ -119,6 +119,15 @@ class _on:
 SCAN_BYTES_PER_ELEMENT = {"scan_fwd": 8, "scan_bwd": 16, "scan_gelu_fwd": 12, "scan_gelu_bwd": 20}
 SCAN_ENTRY_POINTS = ("scan_gelu_fwd", "scan_gelu_bwd")
 
+def _split_workspace(lib, x, B, nsub, D):
+    return torch.empty(lib.hawk_scan_split_workspace_bytes(B, nsub, D), dtype=torch.uint8, device=x.device)
+
+
+def _split_view_ok(v, T):
+    """y / dy of a time-split scan: consecutive sequences exactly T rows apart (or a single sequence)."""
+    return v.shape[0] == 1 or v.stride(0) == T * v.stride(1)
+
+
 @torch.library.custom_op("hawk_b200::scan_fwd", mutates_args=())
 def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Tensor,
              h0: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -131,6 +140,14 @@ def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
         assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
         gate_bias = gate_bias.contiguous()
     h = torch.empty_like(x)
+    nsub = lib.hawk_scan_split_chunks(B, T, D)
+    if nsub > 1:  # few (sequence, channel group) pairs: cut the sequences so that every SM gets work
+        ws = _split_workspace(lib, x, B, nsub, D)
+        with _on(x, "scan_fwd_split", 3):
+            _lib.check(lib.hawk_scan_fwd_split(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
+                                               _ptr(gate_bias), None, 0, 0, h.data_ptr(), None, nsub, ws.data_ptr(),
+                                               ws.numel(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd_split")
+        return h
     with _on(x, "scan_fwd", 1):
         _lib.check(lib.hawk_scan_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
                                      _ptr(gate_bias), h.data_ptr(), B, T, D, _dt(x), _stream(x)), "hawk_scan_fwd")
@@ -162,6 +179,17 @@ def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
         h0 = h0.contiguous()
     if gate_bias is not None:
         gate_bias = gate_bias.contiguous()
+    nsub = lib.hawk_scan_split_chunks(B, T, D)
+    if nsub > 1:
+        ws = _split_workspace(lib, x, B, nsub, D)
+        with _on(x, "scan_bwd_split", 5):
+            _lib.check(lib.hawk_scan_bwd_split(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
+                                               _ptr(gate_bias), h.data_ptr(), None, 0, 0, go.data_ptr(), dx.data_ptr(),
+                                               dgx.data_ptr(), dga.data_ptr(), None, 0, 0, dlam.data_ptr(),
+                                               dh0.data_ptr(), dgb.data_ptr() if gate_bias is not None else None,
+                                               nsub, ws.data_ptr(), ws.numel(), B, T, D, _dt(x), _stream(x)),
+                       "hawk_scan_bwd_split")
+        return dx, dgx, dga, dlam, dh0, dgb
     with _on(x, "scan_bwd", 2):
         _lib.check(lib.hawk_scan_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(h0),
                                      _ptr(gate_bias), h.data_ptr(), go.data_ptr(), dx.data_ptr(), dgx.data_ptr(),
@@ -240,6 +268,15 @@ def scan_gelu_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torc
         assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
         gate_bias = gate_bias.contiguous()
     h, out = torch.empty_like(x), torch.empty_like(x)
+    nsub = lib.hawk_scan_split_chunks(B, T, D) if _split_view_ok(yv, T) else 1
+    if nsub > 1:
+        ws = _split_workspace(lib, x, B, nsub, D)
+        with _on(x, "scan_gelu_fwd_split", 3):
+            _lib.check(lib.hawk_scan_fwd_split(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None,
+                                               _ptr(gate_bias), yv.data_ptr(), T * yv.stride(1), yv.stride(1),
+                                               h.data_ptr(), out.data_ptr(), nsub, ws.data_ptr(), ws.numel(), B, T, D,
+                                               _dt(x), _stream(x)), "hawk_scan_fwd_split")
+        return h, out
     with _on(x, "scan_gelu_fwd", 1):
         _lib.check(lib.hawk_scan_gelu_fwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(gate_bias),
                                           yv.data_ptr(), yv.stride(0), yv.stride(1), h.data_ptr(), out.data_ptr(),
@@ -274,6 +311,18 @@ def scan_gelu_bwd_into(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam:
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     if gate_bias is not None:
         gate_bias = gate_bias.contiguous()
+    nsub = lib.hawk_scan_split_chunks(B, T, D) if (_split_view_ok(yv, T) and _split_view_ok(dy_out, T)) else 1
+    if nsub > 1:
+        ws = _split_workspace(lib, x, B, nsub, D)
+        with _on(x, "scan_gelu_bwd_split", 5):
+            _lib.check(lib.hawk_scan_bwd_split(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), None,
+                                               _ptr(gate_bias), h.data_ptr(), yv.data_ptr(), T * yv.stride(1),
+                                               yv.stride(1), dout.data_ptr(), dx.data_ptr(), dgx.data_ptr(),
+                                               dga.data_ptr(), dy_out.data_ptr(), T * dy_out.stride(1),
+                                               dy_out.stride(1), dlam.data_ptr(), None,
+                                               dgb.data_ptr() if gate_bias is not None else None, nsub, ws.data_ptr(),
+                                               ws.numel(), B, T, D, _dt(x), _stream(x)), "hawk_scan_bwd_split")
+        return dx, dgx, dga, dlam, dgb
     with _on(x, "scan_gelu_bwd", 2):
         _lib.check(lib.hawk_scan_gelu_bwd(x.data_ptr(), gx.data_ptr(), ga.data_ptr(), lam.data_ptr(), _ptr(gate_bias),
                                           h.data_ptr(), yv.data_ptr(), yv.stride(0), yv.stride(1), dout.data_ptr(),

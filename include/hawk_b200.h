@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define HAWK_B200_ABI_VERSION 3
+#define HAWK_B200_ABI_VERSION 4
 
 typedef enum hawk_dtype { HAWK_F32 = 0, HAWK_BF16 = 1 } hawk_dtype;
 
@@ -100,6 +100,32 @@ int hawk_scan_gelu_bwd(const void* x, const void* gx, const void* ga, const floa
                        int64_t y_row_stride, const void* dout, void* dx, void* dgx, void* dga, void* dy,
                        int64_t dy_batch_stride, int64_t dy_row_stride, float* dlam, float* dgate_bias,
                        void* workspace, size_t workspace_bytes, int B, int T, int D, int dtype, void* stream);
+
+/* Time-split scans: the same results as hawk_scan_fwd / hawk_scan_gelu_fwd and hawk_scan_bwd /
+ * hawk_scan_gelu_bwd for launches with few (sequence, channel group) pairs -- one long sequence, a narrow
+ * model -- where a whole-sequence scan leaves most SMs idle (the reference walks T in one warp per channel
+ * block whatever the shape, hawk/scan_fused.py:83).  Every sequence is cut into nsub sub-sequences of
+ * T / nsub rows (T % nsub == 0, nsub <= 64); a first pass reduces each to its affine state map, a small
+ * kernel composes the maps along the sequence, and the ordinary kernels then run over all B * nsub
+ * sub-sequences at once.  Inputs are read twice; results agree with the whole-sequence entry points to
+ * fp32 rounding of the carried state.
+ * hawk_scan_split_chunks: the nsub this library would use for a shape (1: call the whole-sequence entry
+ * points).  y == NULL (and out / dy == NULL) selects the plain scan, otherwise the fused gelu(y) * h
+ * epilogue; y / dy views need batch stride == T * row stride (else HAWK_ERR_UNSUPPORTED).  go is d loss /
+ * d h for the plain scan and d loss / d out for the fused one.  Workspace: 16-byte aligned,
+ * hawk_scan_split_workspace_bytes(B, nsub, D) bytes, no initialisation needed. */
+int hawk_scan_split_chunks(int B, int T, int D);
+size_t hawk_scan_split_workspace_bytes(int B, int nsub, int D);
+int hawk_scan_fwd_split(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                        const float* gate_bias, const void* y, int64_t y_batch_stride, int64_t y_row_stride,
+                        void* h, void* out, int nsub, void* workspace, size_t workspace_bytes, int B, int T,
+                        int D, int dtype, void* stream);
+int hawk_scan_bwd_split(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
+                        const float* gate_bias, const void* h, const void* y, int64_t y_batch_stride,
+                        int64_t y_row_stride, const void* go, void* dx, void* dgx, void* dga, void* dy,
+                        int64_t dy_batch_stride, int64_t dy_row_stride, float* dlam, float* dh0,
+                        float* dgate_bias, int nsub, void* workspace, size_t workspace_bytes, int B, int T,
+                        int D, int dtype, void* stream);
 
 /* hawk_scan_bwd for hosts that cannot allocate device memory (no counterpart in the reference, which
  * allocates its scratch with torch.empty on every call, hawk/scan_fused.py:378).  Same arguments and
