@@ -1072,10 +1072,14 @@ static int split_view(const void* p, int64_t bs, int64_t ld, int T, int L, int D
 }
 }  // namespace hawk
 
-extern "C" int hawk_scan_split_chunks(int B, int T, int D) {
+extern "C" int hawk_scan_split_chunks(int B, int T, int D, int pass) {
   if (B < 1 || T < 1 || D < 64) return 1;
-  const int64_t ctas = (int64_t)B * (D / 32);  // of the whole-sequence launch at its widest shape
-  if (ctas > 64) return 1;                     // at least ~0.4 CTAs per SM already: reading twice costs more
+  // CTAs of the whole-sequence launch at its narrowest shape: 16 channels per CTA for the plain forward, 32 for
+  // the forward with the epilogue and for the backward.  Measured on B200 (bf16, T = 65536): with 64 such CTAs
+  // the split is 1.5-1.7x faster (the plain forward at 128 CTAs is not: 0.35 against 0.38 ms), with 16 CTAs
+  // 2.9-5.7x; at 128 CTAs the whole-sequence kernels already run at 4.4 TB/s and reading twice costs more.
+  if ((int64_t)B * (D / (pass == HAWK_SCAN_PASS_FWD ? 16 : 32)) > 64) return 1;
+  const int64_t ctas = (int64_t)B * (D / 32);  // per sub-sequence in the split launches
   const int want = (int)((2 * 148 + ctas - 1) / ctas);
   for (int n = want; n <= kSplitMaxSub; ++n)
     if (T % n == 0 && T / n >= kSplitMinRows) return n;

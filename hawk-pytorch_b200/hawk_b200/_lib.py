@@ -28,7 +28,7 @@ SIGNATURES = {
     "hawk_scan_gelu_bwd": (c_int, [_P] * 7 + [c_int64, c_int64] + [_P] * 5 + [c_int64, c_int64, _P, _P, _P, c_size_t,
                                   c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_noalloc": (c_int, [_P] * 12 + [c_int, c_int, c_int, c_int, _P]),
-    "hawk_scan_split_chunks": (c_int, [c_int, c_int, c_int]),
+    "hawk_scan_split_chunks": (c_int, [c_int, c_int, c_int, c_int]),
     "hawk_scan_split_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "hawk_scan_fwd_split": (c_int, [_P] * 7 + [c_int64, c_int64, _P, _P, c_int, _P, c_size_t, c_int, c_int, c_int, c_int, _P]),
     "hawk_scan_bwd_split": (c_int, [_P] * 8 + [c_int64, c_int64] + [_P] * 5 + [c_int64, c_int64, _P, _P, _P, c_int, _P,

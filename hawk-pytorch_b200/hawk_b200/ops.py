@@ -140,7 +140,7 @@ def scan_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
         assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
         gate_bias = gate_bias.contiguous()
     h = torch.empty_like(x)
-    nsub = lib.hawk_scan_split_chunks(B, T, D)
+    nsub = lib.hawk_scan_split_chunks(B, T, D, 0)
     if nsub > 1:  # few (sequence, channel group) pairs: cut the sequences so that every SM gets work
         ws = _split_workspace(lib, x, B, nsub, D)
         with _on(x, "scan_fwd_split", 3):
@@ -179,7 +179,7 @@ def scan_bwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torch.Ten
         h0 = h0.contiguous()
     if gate_bias is not None:
         gate_bias = gate_bias.contiguous()
-    nsub = lib.hawk_scan_split_chunks(B, T, D)
+    nsub = lib.hawk_scan_split_chunks(B, T, D, 2)
     if nsub > 1:
         ws = _split_workspace(lib, x, B, nsub, D)
         with _on(x, "scan_bwd_split", 5):
@@ -268,7 +268,7 @@ def scan_gelu_fwd(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam: torc
         assert gate_bias.shape == (2, D) and gate_bias.dtype == torch.float32, "gate_bias: [2, D] fp32"
         gate_bias = gate_bias.contiguous()
     h, out = torch.empty_like(x), torch.empty_like(x)
-    nsub = lib.hawk_scan_split_chunks(B, T, D) if _split_view_ok(yv, T) else 1
+    nsub = lib.hawk_scan_split_chunks(B, T, D, 1) if _split_view_ok(yv, T) else 1
     if nsub > 1:
         ws = _split_workspace(lib, x, B, nsub, D)
         with _on(x, "scan_gelu_fwd_split", 3):
@@ -311,7 +311,7 @@ def scan_gelu_bwd_into(x: torch.Tensor, gx: torch.Tensor, ga: torch.Tensor, lam:
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     if gate_bias is not None:
         gate_bias = gate_bias.contiguous()
-    nsub = lib.hawk_scan_split_chunks(B, T, D) if (_split_view_ok(yv, T) and _split_view_ok(dy_out, T)) else 1
+    nsub = lib.hawk_scan_split_chunks(B, T, D, 2) if (_split_view_ok(yv, T) and _split_view_ok(dy_out, T)) else 1
     if nsub > 1:
         ws = _split_workspace(lib, x, B, nsub, D)
         with _on(x, "scan_gelu_bwd_split", 5):

@@ -109,12 +109,15 @@ int hawk_scan_gelu_bwd(const void* x, const void* gx, const void* ga, const floa
  * kernel composes the maps along the sequence, and the ordinary kernels then run over all B * nsub
  * sub-sequences at once.  Inputs are read twice; results agree with the whole-sequence entry points to
  * fp32 rounding of the carried state.
- * hawk_scan_split_chunks: the nsub this library would use for a shape (1: call the whole-sequence entry
- * points).  y == NULL (and out / dy == NULL) selects the plain scan, otherwise the fused gelu(y) * h
+ * hawk_scan_split_chunks: the nsub this library would use for a shape and pass (HAWK_SCAN_PASS_*; 1: call
+ * the whole-sequence entry point).  y == NULL (and out / dy == NULL) selects the plain scan, otherwise the fused gelu(y) * h
  * epilogue; y / dy views need batch stride == T * row stride (else HAWK_ERR_UNSUPPORTED).  go is d loss /
  * d h for the plain scan and d loss / d out for the fused one.  Workspace: 16-byte aligned,
  * hawk_scan_split_workspace_bytes(B, nsub, D) bytes, no initialisation needed. */
-int hawk_scan_split_chunks(int B, int T, int D);
+#define HAWK_SCAN_PASS_FWD 0      /* plain forward */
+#define HAWK_SCAN_PASS_FWD_GELU 1 /* forward with the gelu(y) * h epilogue */
+#define HAWK_SCAN_PASS_BWD 2      /* either backward */
+int hawk_scan_split_chunks(int B, int T, int D, int pass);
 size_t hawk_scan_split_workspace_bytes(int B, int nsub, int D);
 int hawk_scan_fwd_split(const void* x, const void* gx, const void* ga, const float* lam, const float* h0,
                         const float* gate_bias, const void* y, int64_t y_batch_stride, int64_t y_row_stride,

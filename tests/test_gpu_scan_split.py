@@ -158,11 +158,16 @@ def test_split_rejects_bad_arguments():
 def test_library_chooses_to_split_small_launches():
     from hawk_b200 import _lib
     lib = _lib.load()
-    assert lib.hawk_scan_split_chunks(8, 4096, 2048) == 1       # the benchmark's shape: 512 CTAs already
-    assert lib.hawk_scan_split_chunks(1, 65536, 4096) == 1      # 128 CTAs: reading twice would cost more
-    n = lib.hawk_scan_split_chunks(1, 65536, 512)
-    assert n > 1 and 65536 % n == 0 and 65536 // n >= 256
-    assert lib.hawk_scan_split_chunks(1, 1021, 512) == 1        # a prime number of rows cannot be cut evenly
+    FWD, FWD_GELU, BWD = 0, 1, 2
+    for which in (FWD, FWD_GELU, BWD):
+        assert lib.hawk_scan_split_chunks(8, 4096, 2048, which) == 1       # the benchmark's shape: 512 CTAs already
+        assert lib.hawk_scan_split_chunks(1, 65536, 4096, which) == 1      # 128+ CTAs: reading twice would cost more
+        n = lib.hawk_scan_split_chunks(1, 65536, 512, which)
+        assert n > 1 and 65536 % n == 0 and 65536 // n >= 256
+        assert lib.hawk_scan_split_chunks(1, 1021, 512, which) == 1        # a prime number of rows cannot be cut evenly
+    # 64 CTAs of 32 channels: the backward and the fused forward split, the plain forward (128 CTAs of 16) does not
+    assert lib.hawk_scan_split_chunks(1, 65536, 2048, FWD) == 1
+    assert lib.hawk_scan_split_chunks(1, 65536, 2048, FWD_GELU) > 1 and lib.hawk_scan_split_chunks(1, 65536, 2048, BWD) > 1
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
