@@ -24,6 +24,7 @@
 // out next to h; the backward takes d out in place of d h, forms d h = d out * gelu(y) in its first
 // phase and writes d y = d out * gelu'(y) * h_t (h_t recomputed from the stored h_{t-1}) next to the
 // other gradients.  The separate gelu(y) * h pass over [B,T,D] in each direction disappears.
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -1080,7 +1081,7 @@ extern "C" int hawk_scan_split_chunks(int B, int T, int D, int pass) {
   // 2.9-5.7x; at 128 CTAs the whole-sequence kernels already run at 4.4 TB/s and reading twice costs more.
   if ((int64_t)B * (D / (pass == HAWK_SCAN_PASS_FWD ? 16 : 32)) > 64) return 1;
   const int64_t ctas = (int64_t)B * (D / 32);  // per sub-sequence in the split launches
-  const int want = (int)((2 * 148 + ctas - 1) / ctas);
+  const int want = (int)std::min<int64_t>((2 * 148 + ctas - 1) / ctas, kSplitMaxSub);
   for (int n = want; n <= kSplitMaxSub; ++n)
     if (T % n == 0 && T / n >= kSplitMinRows) return n;
   for (int n = want - 1; n >= 2; --n)

@@ -205,8 +205,10 @@ def test_scan_is_deterministic():
 
 def test_scan_metric_shape_properties():
     """B=8, T=4096, D=2048 bf16 (too large for the CPU oracle in seconds): size-independent checks.
-    (1) time-locality: h[:, :t] does not depend on inputs after t; (2) a channel slice scanned alone
-    gives the same bits; (3) a sampled set of channels matches the fp64 oracle."""
+    (1) time-locality: h[:, :t] does not depend on inputs after t; (2) a channel slice scanned alone gives
+    the same h up to last-bit bf16 roundings (that launch has few channel groups and is cut in time across
+    CTAs, which associates the fp32 recurrence differently); (3) a sampled set of channels matches the fp64
+    oracle."""
     from hawk_b200 import fused_linear_scan
     B, T, D = 8, 4096, 2048
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -222,7 +224,7 @@ def test_scan_metric_shape_properties():
     # (2)
     sl = slice(640, 704)
     h_sl = fused_linear_scan(x[..., sl].contiguous(), gx[..., sl].contiguous(), ga[..., sl].contiguous(), lam[sl].contiguous())
-    assert torch.equal(h_sl, h[..., sl])
+    assert rel_l2(h_sl.float(), h[..., sl].detach().float()) <= 2e-3
     # (3)
     idx = torch.tensor([0, 1, 63, 64, 777, 1024, 2046, 2047])
     cx, cgx, cga, cgo = (t[:2][..., idx.cuda()].float().cpu() for t in (x, gx, ga, go))
@@ -237,8 +239,8 @@ def test_scan_metric_shape_properties():
 
 def test_scan_long_sequence_shape_properties():
     """B=1, T=65536, D=4096 bf16 (the long-sequence stress shape; 268 M elements): (1) time-locality over a
-    prefix that ends inside a super-step; (2) a 64-channel slice scanned alone gives the same bits in the
-    forward; (3) sampled channels match the fp64 oracle over all 65536 steps, forward and backward, with
+    prefix that ends inside a super-step; (2) a 64-channel slice scanned alone (a launch small enough to be cut
+    in time across CTAs) gives the same h up to last-bit bf16 roundings; (3) sampled channels match the fp64 oracle over all 65536 steps, forward and backward, with
     gate biases inside the kernel."""
     from hawk_b200 import fused_linear_scan
     B, T, D = 1, 65536, 4096
@@ -260,7 +262,7 @@ def test_scan_long_sequence_shape_properties():
     sl = slice(2048, 2112)
     h_sl = fused_linear_scan(x[..., sl].contiguous(), gx[..., sl].contiguous(), ga[..., sl].contiguous(),
                              lam[sl].contiguous(), gate_bias=gb[:, sl].contiguous())
-    assert torch.equal(h_sl, h.detach()[..., sl])
+    assert rel_l2(h_sl.float(), h.detach()[..., sl].float()) <= 2e-3
     # (3)
     idx = torch.tensor([0, 65, 2047, 4095])
     ic = idx.cuda()

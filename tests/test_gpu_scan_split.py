@@ -165,6 +165,9 @@ def test_library_chooses_to_split_small_launches():
         n = lib.hawk_scan_split_chunks(1, 65536, 512, which)
         assert n > 1 and 65536 % n == 0 and 65536 // n >= 256
         assert lib.hawk_scan_split_chunks(1, 1021, 512, which) == 1        # a prime number of rows cannot be cut evenly
+    for T in (65536, 4096, 300, 255):  # whatever the shape, the answer is one the split entry points accept
+        n = lib.hawk_scan_split_chunks(1, T, 64, BWD)
+        assert 1 <= n <= 64 and T % n == 0 and (n == 1 or T // n >= 256)
     # 64 CTAs of 32 channels: the backward and the fused forward split, the plain forward (128 CTAs of 16) does not
     assert lib.hawk_scan_split_chunks(1, 65536, 2048, FWD) == 1
     assert lib.hawk_scan_split_chunks(1, 65536, 2048, FWD_GELU) > 1 and lib.hawk_scan_split_chunks(1, 65536, 2048, BWD) > 1
