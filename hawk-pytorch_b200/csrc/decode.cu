@@ -4,6 +4,8 @@
 // [conv_state | x] plus the torch.roll cache update hawk/cache.py:37-43, and hawk/hawk.py:137-151,
 // 193-198 gates -> a -> h = a*state + x~ -> cache write) by two fused elementwise kernels around the
 // block-diagonal gate GEMMs.  Both are one read and one write of [B,D]-sized state: HBM/launch bound.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace hawk {
@@ -223,6 +225,141 @@ decode_block_step_kernel(const T* __restrict__ xy, int64_t ld_xy, TS* __restrict
   }
 }
 
+// The same launch for bf16 activations and bf16 gate weights with the gate products on the tensor cores
+// (mma.sync m16n8k16: a tile of 16 batch rows x 2*BW outputs x BW is far below what tcgen05 tiles want).
+// In the kernel above the products are 2 * 16 * BW * BW scalar MACs per CTA and, with the per-element
+// softplus / exp / erf, 13 M warp instructions per launch: issue bound at 28 us.  Here the conv outputs are
+// rounded to bf16 (as the reference's bf16 conv output is) and sit in shared memory as the A operand
+// [16][BW], each gate's [BW][BW] weight block as the B operand read with ldmatrix.trans; rows are padded by
+// 16 bytes so that the eight row addresses of an ldmatrix fall in different banks.  softplus(Lambda) is
+// computed once per channel and the gates use the MUFU forms of the bf16 scan.
+template <typename TS, int BW>
+__global__ void __launch_bounds__(256)
+decode_block_step_mma_kernel(const __nv_bfloat16* __restrict__ xy, int64_t ld_xy, TS* __restrict__ conv_state,
+                             const float* __restrict__ cw, const float* __restrict__ cb,
+                             const __nv_bfloat16* __restrict__ wx, const __nv_bfloat16* __restrict__ wa,
+                             const float* __restrict__ bx, const float* __restrict__ ba, const float* __restrict__ lam,
+                             TS* __restrict__ state, __nv_bfloat16* __restrict__ out, int B, int R, int W) {
+  using bf = __nv_bfloat16;
+  constexpr int TB = kDecTB, KP = BW + 8, IT = TB * BW / 256 > 0 ? TB * BW / 256 : 1;
+  static_assert(BW % 16 == 0 && BW <= 128 && TB == 16, "one m16 tile of batch rows, k in steps of 16");
+  extern __shared__ __align__(16) unsigned char dsm_raw[];
+  bf* xcb = reinterpret_cast<bf*>(dsm_raw);                 // [TB][KP]      conv outputs (A operand)
+  bf* ws = xcb + TB * KP;                                   // [2][BW][KP]   the block's two weight matrices (B operands)
+  float* g = reinterpret_cast<float*>(ws + 2 * BW * KP);    // [2][TB][BW]   gate pre-activations
+  float* spc = g + 2 * TB * BW;                             // [BW]          softplus(Lambda)
+  const int blk = blockIdx.x, b0 = blockIdx.y * TB, ch0 = blk * BW;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  // every global input is requested before anything waits (see the kernel above)
+  constexpr int nelem = TB * BW;
+  float xn[IT], yv[IT], sv[IT], cacc[IT], win[IT][3];
+  bool ok[IT];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int idx = threadIdx.x + it * 256;
+    const int b = idx / BW, c = idx % BW, bg = b0 + b, ch = ch0 + c;
+    ok[it] = idx < nelem && bg < B;
+    xn[it] = yv[it] = sv[it] = cacc[it] = 0.f;
+    win[it][0] = win[it][1] = win[it][2] = 0.f;
+    if (ok[it]) {
+      const bf* xr = xy + (int64_t)bg * ld_xy;
+      xn[it] = to_float(xr[ch]);
+      yv[it] = to_float(xr[R + ch]);
+      sv[it] = to_float(state[(int64_t)bg * R + ch]);
+      const TS* sp = conv_state + ((int64_t)bg * (W - 1)) * R + ch;
+      float acc = fmaf(cw[(int64_t)(W - 1) * R + ch], xn[it], cb[ch]);
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        if (j < W - 1) {
+          win[it][j] = to_float(sp[(int64_t)j * R]);
+          acc = fmaf(cw[(int64_t)j * R + ch], win[it][j], acc);
+        }
+      }
+      cacc[it] = acc;
+    }
+  }
+  {  // weights: rows of BW elements into rows of KP, 16 bytes at a time (global rows are 16-byte aligned: host check)
+    constexpr int Q = BW / 8;
+    const uint4* s0 = reinterpret_cast<const uint4*>(wx + (int64_t)blk * BW * BW);
+    const uint4* s1 = reinterpret_cast<const uint4*>(wa + (int64_t)blk * BW * BW);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < BW * Q; i += 256) {
+      const int k = i / Q, q = i % Q;
+      *reinterpret_cast<uint4*>(ws + k * KP + q * 8) = __ldg(s0 + i);
+      *reinterpret_cast<uint4*>(ws + (BW + k) * KP + q * 8) = __ldg(s1 + i);
+    }
+  }
+  if (threadIdx.x < BW) {
+    const float l = lam[ch0 + threadIdx.x];
+    spc[threadIdx.x] = l > 20.f ? l : softplus_f(l);
+  }
+  // conv outputs (rounded to bf16) to shared memory, and the cache roll (hawk/hawk.py:168-179, hawk/cache.py:37-43)
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int idx = threadIdx.x + it * 256;
+    const int b = idx / BW, c = idx % BW;
+    if (idx < nelem) xcb[b * KP + c] = __float2bfloat16(cacc[it]);
+    if (ok[it]) {
+      TS* sp = conv_state + ((int64_t)(b0 + b) * (W - 1)) * R + ch0 + c;
+#pragma unroll
+      for (int j = 1; j < 3; ++j)
+        if (j < W - 1) sp[(int64_t)(j - 1) * R] = from_float<TS>(win[it][j]);
+      if (W > 1) sp[(int64_t)(W - 2) * R] = from_float<TS>(xn[it]);
+    }
+  }
+  __syncthreads();
+
+  // both gate projections: g[gate][b][j] = bias[j] + sum_k xc[b][k] w[gate][k][j]  (external.py:224-233)
+  {
+    constexpr int KS = BW / 16, NT = 2 * BW / 8;
+    uint32_t afrag[KS][4];
+    const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(xcb + (lane & 15) * KP + (lane >> 4) * 8);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(afrag[ks][0]), "=r"(afrag[ks][1]), "=r"(afrag[ks][2]), "=r"(afrag[ks][3])
+                   : "r"(a_addr + ks * 32));
+    const int gid = lane >> 2, tig = lane & 3;
+    for (int t = warp; t < NT; t += 8) {
+      const int gate = (t * 8) / BW, n0 = t * 8 - gate * BW;
+      const uint32_t b_addr = (uint32_t)__cvta_generic_to_shared(ws + (gate * BW + (lane & 15)) * KP + n0);
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t b0r, b1r;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                     : "=r"(b0r), "=r"(b1r)
+                     : "r"(b_addr + ks * 16 * KP * 2));
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(afrag[ks][0]), "r"(afrag[ks][1]), "r"(afrag[ks][2]), "r"(afrag[ks][3]), "r"(b0r), "r"(b1r));
+      }
+      const float2 bias = *reinterpret_cast<const float2*>((gate ? ba : bx) + ch0 + n0 + 2 * tig);
+      float* gp = g + ((size_t)gate * TB + gid) * BW + n0 + 2 * tig;
+      *reinterpret_cast<float2*>(gp) = make_float2(c[0] + bias.x, c[1] + bias.y);
+      *reinterpret_cast<float2*>(gp + 8 * BW) = make_float2(c[2] + bias.x, c[3] + bias.y);
+    }
+  }
+  __syncthreads();
+
+  // RG-LRU step (hawk/hawk.py:137-151,193-198) and the output gate gelu(y) * h (:134-135)
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    if (!ok[it]) continue;
+    const int idx = threadIdx.x + it * 256;
+    const int b = idx / BW, c = idx % BW;
+    const float i = sigmoid_f<true>(g[(size_t)b * BW + c]);
+    const float r = sigmoid_f<true>(g[((size_t)TB + b) * BW + c]);
+    const float a = ex2_approx(kLog2e * (kGateC * r * spc[c]));
+    const float m = sqrt_approx(fmaxf(1.f - a * a, 0.f));
+    const int64_t so = (int64_t)(b0 + b) * R + ch0 + c;
+    const float h = fmaf(a, sv[it], (cacc[it] * i) * m);
+    state[so] = from_float<TS>(h);
+    out[so] = __float2bfloat16(gelu_f(yv[it]) * h);
+  }
+}
+
 template <typename T, typename TS>
 static int conv_step_dispatch(const void* x_new, int64_t xrs, void* conv_state, const float* w, const float* bias,
                               void* y, int B, int D, int W, cudaStream_t st) {
@@ -299,8 +436,32 @@ template <typename T, typename TS, typename TW>
 static int block_step_launch(const void* xy, int64_t ld_xy, void* conv_state, const float* cw, const float* cb,
                              const void* wx, const void* wa, const float* bx, const float* ba, const float* lam,
                              void* state, void* out, int B, int R, int bw, int W, cudaStream_t st) {
-  const size_t smem = (size_t)3 * kDecTB * bw * sizeof(float) + (size_t)2 * bw * bw * sizeof(TW);
   dim3 grid((unsigned)(R / bw), (unsigned)((B + kDecTB - 1) / kDecTB));
+  if constexpr (std::is_same<T, __nv_bfloat16>::value && std::is_same<TW, __nv_bfloat16>::value) {
+    const bool rows16 = aligned(wx, 16) && aligned(wa, 16) && aligned(bx, 8) && aligned(ba, 8);
+    if (rows16 && (bw == 128 || bw == 64 || bw == 32 || bw == 16)) {
+#define HAWK_DEC_MMA(BWV)                                                                                            \
+  do {                                                                                                               \
+    constexpr int smem_mma = (kDecTB * (BWV + 8) + 2 * BWV * (BWV + 8)) * 2 + (2 * kDecTB * BWV + BWV) * 4;            \
+    auto kmma = decode_block_step_mma_kernel<TS, BWV>;                                                               \
+    if (smem_mma > 48 * 1024 &&                                                                                      \
+        cudaFuncSetAttribute(kmma, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_mma) != cudaSuccess) {          \
+      (void)cudaGetLastError();                                                                                      \
+      return HAWK_ERR_LAUNCH;                                                                                        \
+    }                                                                                                                \
+    kmma<<<grid, 256, smem_mma, st>>>(static_cast<const __nv_bfloat16*>(xy), ld_xy, static_cast<TS*>(conv_state), cw, \
+                                      cb, static_cast<const __nv_bfloat16*>(wx), static_cast<const __nv_bfloat16*>(wa), \
+                                      bx, ba, lam, static_cast<TS*>(state), static_cast<__nv_bfloat16*>(out), B, R, W); \
+    return launch_status();                                                                                          \
+  } while (0)
+      if (bw == 128) HAWK_DEC_MMA(128);
+      if (bw == 64) HAWK_DEC_MMA(64);
+      if (bw == 32) HAWK_DEC_MMA(32);
+      HAWK_DEC_MMA(16);
+#undef HAWK_DEC_MMA
+    }
+  }
+  const size_t smem = (size_t)3 * kDecTB * bw * sizeof(float) + (size_t)2 * bw * bw * sizeof(TW);
   auto kern = decode_block_step_kernel<T, TS, TW>;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

@@ -67,13 +67,28 @@ class RMSNorm(nn.Module):
         # under autocast the only consumer is a Linear, which would round its input to bf16 anyway
         return torch.bfloat16 if (x.is_cuda and torch.is_autocast_enabled("cuda")) else None
 
+    def _weight32(self):
+        """The kernels take the weight in fp32.  A model converted to bf16 for inference would otherwise pay a
+        cast launch per norm per token (49 of a decode step's 244 launches): keep an fp32 copy, remade when
+        the weight is written (version counter) or replaced."""
+        w = self.weight
+        if w.dtype == torch.float32:
+            return w
+        if w.requires_grad and torch.is_grad_enabled():
+            return w.float()  # training a reduced-precision weight: keep the cast in the autograd graph
+        key = (w.data_ptr(), w._version, w.device)
+        if getattr(self, "_w32_key", None) != key:
+            self._w32 = w.detach().float()
+            self._w32_key = key
+        return self._w32
+
     def forward(self, x):
-        return ops.rms_norm(x, self.weight, self.eps, out_dtype=self._out_dtype(x))
+        return ops.rms_norm(x, self._weight32(), self.eps, out_dtype=self._out_dtype(x))
 
     def add_forward(self, residual, delta):
         """(residual + delta, norm(residual + delta)); delta None = plain norm.  The residual add that
         precedes every norm (hawk/hawk.py:229,234) is fused into it."""
-        return ops.add_rms_norm(residual, delta, self.weight, self.eps, out_dtype=self._out_dtype(residual))
+        return ops.add_rms_norm(residual, delta, self._weight32(), self.eps, out_dtype=self._out_dtype(residual))
 
 
 class BlockDiagonalLinear(nn.Module):
