@@ -241,7 +241,7 @@ decode_block_step_mma_kernel(const __nv_bfloat16* __restrict__ xy, int64_t ld_xy
                              const float* __restrict__ bx, const float* __restrict__ ba, const float* __restrict__ lam,
                              TS* __restrict__ state, __nv_bfloat16* __restrict__ out, int B, int R, int W) {
   using bf = __nv_bfloat16;
-  constexpr int TB = kDecTB, KP = BW + 8, IT = TB * BW / 256 > 0 ? TB * BW / 256 : 1;
+  constexpr int TB = kDecTB, KP = BW + 8;
   static_assert(BW % 16 == 0 && BW <= 128 && TB == 16, "one m16 tile of batch rows, k in steps of 16");
   extern __shared__ __align__(16) unsigned char dsm_raw[];
   bf* xcb = reinterpret_cast<bf*>(dsm_raw);                 // [TB][KP]      conv outputs (A operand)
@@ -251,32 +251,37 @@ decode_block_step_mma_kernel(const __nv_bfloat16* __restrict__ xy, int64_t ld_xy
   const int blk = blockIdx.x, b0 = blockIdx.y * TB, ch0 = blk * BW;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-  // every global input is requested before anything waits (see the kernel above)
-  constexpr int nelem = TB * BW;
-  float xn[IT], yv[IT], sv[IT], cacc[IT], win[IT][3];
-  bool ok[IT];
+  // A thread owns 8 consecutive channels of one batch row (TB * BW / 8 <= 256 threads have work): every
+  // global input arrives as 16-byte loads, all requested before anything waits.
+  constexpr int VEC = 8, TPR = BW / VEC;  // threads per batch row
+  const int eb = threadIdx.x / TPR, ec = (threadIdx.x % TPR) * VEC;
+  const bool has = threadIdx.x < TB * TPR, ok = has && b0 + eb < B;
+  float xn[VEC], yv[VEC], sv[VEC], cacc[VEC], win[3][VEC];
 #pragma unroll
-  for (int it = 0; it < IT; ++it) {
-    const int idx = threadIdx.x + it * 256;
-    const int b = idx / BW, c = idx % BW, bg = b0 + b, ch = ch0 + c;
-    ok[it] = idx < nelem && bg < B;
-    xn[it] = yv[it] = sv[it] = cacc[it] = 0.f;
-    win[it][0] = win[it][1] = win[it][2] = 0.f;
-    if (ok[it]) {
-      const bf* xr = xy + (int64_t)bg * ld_xy;
-      xn[it] = to_float(xr[ch]);
-      yv[it] = to_float(xr[R + ch]);
-      sv[it] = to_float(state[(int64_t)bg * R + ch]);
-      const TS* sp = conv_state + ((int64_t)bg * (W - 1)) * R + ch;
-      float acc = fmaf(cw[(int64_t)(W - 1) * R + ch], xn[it], cb[ch]);
+  for (int v = 0; v < VEC; ++v) xn[v] = yv[v] = sv[v] = cacc[v] = win[0][v] = win[1][v] = win[2][v] = 0.f;
+  if (ok) {
+    const int64_t bg = b0 + eb;
+    const int ch = ch0 + ec;
+    const bf* xr = xy + bg * ld_xy;
+    VecIO<bf, VEC>::load(xr + ch, xn);
+    VecIO<bf, VEC>::load(xr + R + ch, yv);
+    VecIO<TS, VEC>::load(state + bg * R + ch, sv);
+    const TS* sp = conv_state + (bg * (W - 1)) * R + ch;
 #pragma unroll
-      for (int j = 0; j < 3; ++j) {
-        if (j < W - 1) {
-          win[it][j] = to_float(sp[(int64_t)j * R]);
-          acc = fmaf(cw[(int64_t)j * R + ch], win[it][j], acc);
-        }
+    for (int j = 0; j < 3; ++j)
+      if (j < W - 1) VecIO<TS, VEC>::load(sp + (int64_t)j * R, win[j]);
+    float wv[VEC];
+    VecIO<float, VEC>::load(cb + ch, cacc);
+    VecIO<float, VEC>::load(cw + (int64_t)(W - 1) * R + ch, wv);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) cacc[v] = fmaf(wv[v], xn[v], cacc[v]);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {  // state row j is x[t-(W-1)+j], paired with w[j]
+      if (j < W - 1) {
+        VecIO<float, VEC>::load(cw + (int64_t)j * R + ch, wv);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) cacc[v] = fmaf(wv[v], win[j][v], cacc[v]);
       }
-      cacc[it] = acc;
     }
   }
   {  // weights: rows of BW elements into rows of KP, 16 bytes at a time (global rows are 16-byte aligned: host check)
@@ -295,18 +300,13 @@ decode_block_step_mma_kernel(const __nv_bfloat16* __restrict__ xy, int64_t ld_xy
     spc[threadIdx.x] = l > 20.f ? l : softplus_f(l);
   }
   // conv outputs (rounded to bf16) to shared memory, and the cache roll (hawk/hawk.py:168-179, hawk/cache.py:37-43)
+  if (has) VecIO<bf, VEC>::store(xcb + eb * KP + ec, cacc);  // rows past the batch hold zeros
+  if (ok) {
+    TS* sp = conv_state + ((int64_t)(b0 + eb) * (W - 1)) * R + ch0 + ec;
 #pragma unroll
-  for (int it = 0; it < IT; ++it) {
-    const int idx = threadIdx.x + it * 256;
-    const int b = idx / BW, c = idx % BW;
-    if (idx < nelem) xcb[b * KP + c] = __float2bfloat16(cacc[it]);
-    if (ok[it]) {
-      TS* sp = conv_state + ((int64_t)(b0 + b) * (W - 1)) * R + ch0 + c;
-#pragma unroll
-      for (int j = 1; j < 3; ++j)
-        if (j < W - 1) sp[(int64_t)(j - 1) * R] = from_float<TS>(win[it][j]);
-      if (W > 1) sp[(int64_t)(W - 2) * R] = from_float<TS>(xn[it]);
-    }
+    for (int j = 1; j < 3; ++j)
+      if (j < W - 1) VecIO<TS, VEC>::store(sp + (int64_t)(j - 1) * R, win[j]);
+    if (W > 1) VecIO<TS, VEC>::store(sp + (int64_t)(W - 2) * R, xn);
   }
   __syncthreads();
 
@@ -344,19 +344,27 @@ decode_block_step_mma_kernel(const __nv_bfloat16* __restrict__ xy, int64_t ld_xy
   __syncthreads();
 
   // RG-LRU step (hawk/hawk.py:137-151,193-198) and the output gate gelu(y) * h (:134-135)
+  if (ok) {
+    float gi[VEC], gr[VEC], sp8[VEC], hv[VEC], ov[VEC];
+    auto lds8 = [](const float* p, float (&v)[VEC]) {  // shared memory: plain loads
+      const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    };
+    lds8(g + (size_t)eb * BW + ec, gi);
+    lds8(g + ((size_t)TB + eb) * BW + ec, gr);
+    lds8(spc + ec, sp8);
 #pragma unroll
-  for (int it = 0; it < IT; ++it) {
-    if (!ok[it]) continue;
-    const int idx = threadIdx.x + it * 256;
-    const int b = idx / BW, c = idx % BW;
-    const float i = sigmoid_f<true>(g[(size_t)b * BW + c]);
-    const float r = sigmoid_f<true>(g[((size_t)TB + b) * BW + c]);
-    const float a = ex2_approx(kLog2e * (kGateC * r * spc[c]));
-    const float m = sqrt_approx(fmaxf(1.f - a * a, 0.f));
-    const int64_t so = (int64_t)(b0 + b) * R + ch0 + c;
-    const float h = fmaf(a, sv[it], (cacc[it] * i) * m);
-    state[so] = from_float<TS>(h);
-    out[so] = __float2bfloat16(gelu_f(yv[it]) * h);
+    for (int v = 0; v < VEC; ++v) {
+      const float i = sigmoid_f<true>(gi[v]);
+      const float r = sigmoid_f<true>(gr[v]);
+      const float a = ex2_approx(kLog2e * (kGateC * r * sp8[v]));
+      const float m = sqrt_approx(fmaxf(1.f - a * a, 0.f));
+      hv[v] = fmaf(a, sv[v], (cacc[v] * i) * m);
+      ov[v] = gelu_f(yv[v]) * hv[v];
+    }
+    const int64_t so = (int64_t)(b0 + eb) * R + ch0 + ec;
+    VecIO<TS, VEC>::store(state + so, hv);
+    VecIO<bf, VEC>::store(out + so, ov);
   }
 }
 
@@ -438,7 +446,9 @@ static int block_step_launch(const void* xy, int64_t ld_xy, void* conv_state, co
                              void* state, void* out, int B, int R, int bw, int W, cudaStream_t st) {
   dim3 grid((unsigned)(R / bw), (unsigned)((B + kDecTB - 1) / kDecTB));
   if constexpr (std::is_same<T, __nv_bfloat16>::value && std::is_same<TW, __nv_bfloat16>::value) {
-    const bool rows16 = aligned(wx, 16) && aligned(wa, 16) && aligned(bx, 8) && aligned(ba, 8);
+    const bool rows16 = aligned(wx, 16) && aligned(wa, 16) && aligned(bx, 8) && aligned(ba, 8) && aligned(xy, 16) &&
+                        ld_xy % 8 == 0 && aligned(conv_state, 16) && aligned(state, 16) && aligned(out, 16) &&
+                        aligned(cw, 16) && aligned(cb, 16);
     if (rows16 && (bw == 128 || bw == 64 || bw == 32 || bw == 16)) {
 #define HAWK_DEC_MMA(BWV)                                                                                            \
   do {                                                                                                               \
