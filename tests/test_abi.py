@@ -160,3 +160,31 @@ def test_fused_scan_and_gate_projection_argument_validation_needs_no_gpu():
     assert lib.hawk_gates_bwd(p, p, p, p, p, p, p, p, need - 1, 4096, 2048, 128, p, None) == -5
     assert lib.hawk_debug_wait_timeout(p, 1024, 100000, p, None) == -5               # scratch too small
     assert lib.hawk_debug_wait_timeout(p, 1 << 20, 10, p, None) == -2                # budget out of range
+
+
+def test_time_split_policy_and_validation_need_no_gpu():
+    """hawk_scan_split_chunks is host arithmetic: its answers are ones the split entry points accept (a divisor of
+    T, at most 64 pieces of at least 256 rows), it leaves launches with enough CTAs alone, and the entry points
+    reject bad splits before touching the device."""
+    lib = L.load()
+    FWD, FWD_GELU, BWD = 0, 1, 2
+    for which in (FWD, FWD_GELU, BWD):
+        for (B, T, D) in [(1, 65536, 64), (1, 65536, 512), (2, 2048, 512), (1, 4096, 256), (3, 8192, 128), (1, 300, 64),
+                          (1, 1021, 512), (8, 4096, 2048), (1, 65536, 4096), (64, 4096, 64)]:
+            n = lib.hawk_scan_split_chunks(B, T, D, which)
+            assert 1 <= n <= 64 and T % n == 0 and (n == 1 or T // n >= 256), (B, T, D, which, n)
+        assert lib.hawk_scan_split_chunks(8, 4096, 2048, which) == 1
+        assert lib.hawk_scan_split_chunks(1, 65536, 4096, which) == 1
+        assert lib.hawk_scan_split_chunks(1, 65536, 512, which) > 1
+        assert lib.hawk_scan_split_chunks(1, 1021, 512, which) == 1  # a prime number of rows cannot be cut evenly
+    # 64 CTAs of 32 channels but 128 of 16: only the plain forward stays whole
+    assert lib.hawk_scan_split_chunks(1, 65536, 2048, FWD) == 1 and lib.hawk_scan_split_chunks(1, 65536, 2048, BWD) > 1
+    assert lib.hawk_scan_split_workspace_bytes(2, 8, 512) == 7 * 2 * 8 * 512 * 4
+    assert lib.hawk_scan_split_workspace_bytes(0, 8, 512) == 0
+    p = ctypes.c_void_p(4096)  # never dereferenced: validation fails first
+    args = lambda nsub, wsb, T=1024: (p, p, p, p, None, None, None, 0, 0, p, None, nsub, p, wsb, 1, T, 64, 1, None)
+    big = 1 << 30
+    assert lib.hawk_scan_fwd_split(*args(3, big)) < 0               # 1024 rows do not split in three
+    assert lib.hawk_scan_fwd_split(*args(65, big, T=65 * 64)) < 0   # more pieces than supported
+    assert lib.hawk_scan_fwd_split(*args(4, 16)) < 0                # workspace too small
+    assert lib.hawk_scan_fwd_split(p, p, p, p, None, None, p, 0, 0, p, None, 4, p, big, 1, 1024, 64, 1, None) < 0  # y without out
