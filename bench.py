@@ -525,6 +525,28 @@ def run_ours(args):
     ops.LOG.reset(enabled=False)
     comm = timeline.summary() if timeline is not None else None  # the gradient all-reduces of the last step
 
+    # ---- N > 1: every rank's own step with the all-reduce switched off (last thing the replicas do together:
+    # they diverge from here).  Tells rank skew and DDP's own overhead apart from communication. ----
+    if world > 1:
+        trainer.step(dev_ids[0], sync_gradients=False)
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for i in range(3):
+            trainer.step(dev_ids[i % 2], sync_gradients=False)
+        c1.record()
+        torch.cuda.synchronize()
+        mine = torch.tensor([c0.elapsed_time(c1) / 3], device=dev, dtype=torch.float64)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        per_rank = [float(t.item()) for t in every]
+        if comm is None:
+            comm = {}
+        comm["compute_only_ms_per_rank"] = [round(v, 2) for v in per_rank]
+        comm["compute_only_what"] = ("ms per step of each rank with the gradient all-reduce switched off (3 steps after "
+                                     "everything else was measured): the synchronised step cannot be faster than the "
+                                     "slowest of these")
+
     if rank != 0:
         return 0
 

@@ -205,10 +205,21 @@ class Trainer:
             self.opt = torch.optim.AdamW(self.model.parameters(), lr=lr, weight_decay=0.1,
                                          fused=self.device.type == "cuda")
 
-    def step(self, ids: torch.Tensor, after_backward=None) -> torch.Tensor:
+    def step(self, ids: torch.Tensor, after_backward=None, sync_gradients: bool = True) -> torch.Tensor:
         """One training step; `after_backward(loss)`, when given, runs between the backward pass (gradients
-        all-reduced) and the optimiser update, e.g. to inspect gradients."""
+        all-reduced) and the optimiser update, e.g. to inspect gradients.  `sync_gradients=False` (multi-GPU
+        measurement only: the replicas diverge) skips the gradient all-reduce, so that a rank's own compute
+        time can be told apart from communication and from waiting for slower ranks."""
         net = self.ddp if self.ddp is not None else self.model
+        if not sync_gradients and self.ddp is not None:
+            with self.ddp.no_sync():
+                with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast):
+                    loss = net(ids, ids)
+                loss.backward()
+            self.opt.step()
+            self.opt.zero_grad(set_to_none=True)
+            self.steps_done += 1
+            return loss.detach()
         with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast):
             loss = net(ids, ids)
         if self.timeline is not None:

@@ -72,6 +72,7 @@ def data(step):
 if __name__ == "__main__":
     out_path = sys.argv[1]
     fail_rank = int(sys.argv[2]) if len(sys.argv) > 2 else -1
+    unsynced_tail = len(sys.argv) > 3 and sys.argv[3] == "unsynced"  # one more step without the all-reduce
     patch_ops()
     rank, _, world = train.init_distributed("gloo")
     tr = make_trainer(world)
@@ -81,5 +82,10 @@ if __name__ == "__main__":
             os._exit(17)  # a rank that dies between steps: the others must fail, not hang
         ids = data(step).chunk(world, dim=0)[rank]  # batch sharding: rank r takes its slice
         losses.append(float(tr.step(ids)))
+    synced = {k: v.detach().clone() for k, v in tr.model.state_dict().items()}
+    if unsynced_tail:
+        tr.step(data(3).chunk(world, dim=0)[rank], sync_gradients=False)
+        torch.save({"synced": synced, "after": {k: v.detach().clone() for k, v in tr.model.state_dict().items()}},
+                   f"{out_path}.tail.{rank}")
     torch.save({"losses": losses, "params": {k: v.detach().clone() for k, v in tr.model.state_dict().items()}},
                f"{out_path}.{rank}")

@@ -54,3 +54,15 @@ def test_dead_rank_is_detected_not_hung(tmp_path):
     outs = _launch(tmp_path, 2, 29633, extra=("1",), timeout=180)
     assert outs[1][0] == 17
     assert outs[0][0] != 0 and "[timeout]" not in outs[0][1], outs[0][1][-500:]
+
+
+def test_step_without_gradient_sync_is_local(tmp_path):
+    """`Trainer.step(sync_gradients=False)` (the benchmark's per-rank compute-only measurement): no collective
+    runs, each rank applies its own gradients, so replicas that were bit-identical differ afterwards."""
+    outs = _launch(tmp_path, 2, 29635, extra=("-1", "unsynced"))
+    assert all(rc == 0 for rc, _ in outs), outs
+    t0, t1 = (torch.load(f"{tmp_path}/out.tail.{r}") for r in range(2))
+    assert all(torch.equal(t0["synced"][k], t1["synced"][k]) for k in t0["synced"])
+    moved = [k for k in t0["after"] if not torch.equal(t0["after"][k], t0["synced"][k])]
+    differ = [k for k in t0["after"] if not torch.equal(t0["after"][k], t1["after"][k])]
+    assert moved and differ  # the step was taken, with rank-local gradients
