@@ -16,7 +16,10 @@ One JSON line is printed by rank 0:
              copy bandwidth of this pool (MEASURED_PEAKS.json, else the 6650 GB/s fallback);
              `isolated` / `isolated_fused` repeat the measurement outside the step on the plain scan
              (24 B/element) and on the fused entry points (N = 1);
-  comm       (N > 1) the gradient all-reduces of one step timed per DDP bucket against the backward pass;
+  comm       (N > 1) the gradient all-reduces of one step timed per DDP bucket against the backward pass, and
+             every rank's own step time with the all-reduce switched off (what the synchronised step is
+             measured against: ranks differ by several ms under the power cap);
+             `--grad-comm-dtype bf16` / `--bucket-mb M` change how the gradients are reduced;
   kernels    mean device time and derived rate of each of this library's entry points, from separate
              instrumented steps after the timed regions;
   parity     the check that is free at the reference initialisation: first-step loss = ln 32000 and only
