@@ -497,6 +497,11 @@ class Conv1D(nn.Module):
     def forward(self, x):
         return temporal_conv1d(x, self.w, self.b, out_dtype=self.out_dtype)
 
+    def doc_mask_forward(self, x):
+        """The reference's name for the same computation (hawk/external.py:49-95; its forward is this method,
+        :97-98; no document mask is applied there either: prompt_len = 0, segment positions unused)."""
+        return self.forward(x)
+
 
 # ---------------------------------------------------------------------------------------------
 # cached decode step

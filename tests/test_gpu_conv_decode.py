@@ -104,6 +104,7 @@ def test_conv_module_has_reference_parameters():
     m = m.cuda()
     x = torch.randn(2, 10, 64, device="cuda")
     assert max_rel(m(x).cpu(), oconv.conv1d_fwd(x.cpu(), m.w.detach().cpu(), m.b.detach().cpu())) <= FP32_TOL
+    assert torch.equal(m.doc_mask_forward(x), m(x))  # the reference's name for the same call (external.py:49,97-98)
 
 
 @pytest.mark.parametrize("B,D", [(1, 64), (3, 72), (256, 2048)])
