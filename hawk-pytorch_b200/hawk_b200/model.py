@@ -54,6 +54,19 @@ def ring_init_(lam: torch.Tensor, min_rad: float = 0.9, max_rad: float = 0.999, 
     return lam
 
 
+def rnn_param_init(tensor: torch.Tensor, min_rad: float, max_rad: float, transform: str = "softplus",
+                   eps: float = 1e-8) -> torch.Tensor:
+    """The reference's name and signature for the ring initialisation (hawk/external.py:153-168)."""
+    if transform != "softplus":
+        raise NotImplementedError()  # as the reference
+    return ring_init_(tensor, min_rad, max_rad, eps)
+
+
+def lecun_init(w: torch.Tensor, d_in: int) -> None:
+    """The reference's name for the N(0, 1/sqrt(d_in)) initialisation (hawk/hawk.py:37-39)."""
+    _lecun_normal_(w, d_in)
+
+
 class RMSNorm(nn.Module):
     """hawk/hawk.py:47-58: statistics in fp32, result in the input dtype, times the weight."""
 

@@ -111,3 +111,17 @@ def test_install_rebinds_the_three_names():
     assert fake_mod.fused_cross_entropy is ops.fused_cross_entropy and fake_mod.Conv1D is ops.Conv1D
     inst.uninstall(pkg)
     assert (fake_mod.fused_linear_scan, fake_mod.fused_cross_entropy, fake_mod.Conv1D) == (1, 2, 3)
+
+
+def test_reference_initialiser_names():
+    """rnn_param_init / lecun_init under the reference's names and signatures (hawk/external.py:153-168,
+    hawk/hawk.py:37-39): exp(-softplus(Lambda)) lands on the [min_rad, max_rad] ring."""
+    torch.manual_seed(0)
+    lam = M.rnn_param_init(torch.empty(4096), 0.9, 0.999)
+    a = torch.exp(-F.softplus(lam.double()))
+    assert float(a.min()) >= 0.9 - 1e-6 and float(a.max()) <= 0.999 + 1e-6
+    with pytest.raises(NotImplementedError):
+        M.rnn_param_init(torch.empty(4), 0.9, 0.999, transform="exp")
+    w = torch.empty(512, 256)
+    M.lecun_init(w, 256)
+    assert abs(float(w.std()) - 1 / math.sqrt(256)) < 0.01 / math.sqrt(256) * 10
