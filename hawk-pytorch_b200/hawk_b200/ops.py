@@ -247,6 +247,21 @@ def fused_linear_scan(x, x_rg_lru, a_rg_lru, a_param, *, h0=None, gate_bias=None
     return scan_fwd(x, x_rg_lru, a_rg_lru, lam, h0, gate_bias)
 
 
+def sequential_scan_forward(x, x_rg_lru, a_rg_lru, a_param):
+    """The reference's host function of the forward (hawk/scan_fused.py:319-360): h for tensors of one dtype, no
+    autograd, no autocast handling.  Non-contiguous inputs are copied where the reference asserts."""
+    lam = a_param if a_param.dtype == torch.float32 else a_param.float()
+    return scan_fwd(x, x_rg_lru, a_rg_lru, lam, None, None)
+
+
+def sequential_scan_backward(x_saved, x_rg_lru_saved, a_rg_lru_saved, a_param_saved, h_saved, grad_out):
+    """The reference's host function of the backward (hawk/scan_fused.py:363-424), same argument order:
+    (x_grad, x_rg_lru_grad, a_rg_lru_grad, a_param_grad), the last in a_param's dtype as there (:378,424)."""
+    lam = a_param_saved if a_param_saved.dtype == torch.float32 else a_param_saved.float()
+    dx, dgx, dga, dlam, _, _ = scan_bwd(x_saved, x_rg_lru_saved, a_rg_lru_saved, lam, None, None, h_saved, grad_out)
+    return dx, dgx, dga, dlam.to(a_param_saved.dtype)
+
+
 def _conv_view(x: torch.Tensor) -> torch.Tensor:
     """x as the kernels can read it in place: [B,T,D], unit channel stride, 16-byte aligned rows."""
     ok = (x.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0

@@ -279,3 +279,19 @@ def test_scan_long_sequence_shape_properties():
     assert rel_l2(lam_r.grad[ic].cpu(), wdlam) <= BF16_TOL
     want_gb = torch.stack((wdgx.sum((0, 1)), wdga.sum((0, 1))))
     assert rel_l2(gb_r.grad[:, ic].cpu(), want_gb) <= BF16_TOL
+
+
+def test_reference_host_function_names():
+    """sequential_scan_forward / sequential_scan_backward with the reference's argument order
+    (hawk/scan_fused.py:319-324,363-370) give what fused_linear_scan and its autograd give."""
+    from hawk_b200 import fused_linear_scan, sequential_scan_backward, sequential_scan_forward
+    x, gx, ga, go, lam = _inputs(2, 130, 128, seed=21)
+    xs = [t.cuda().requires_grad_(True) for t in (x, gx, ga)]
+    lam_d = lam.cuda().requires_grad_(True)
+    h = fused_linear_scan(*xs, lam_d)
+    h.backward(go.cuda())
+    h2 = sequential_scan_forward(x.cuda(), gx.cuda(), ga.cuda(), lam.cuda())
+    assert torch.equal(h2, h.detach())
+    grads = sequential_scan_backward(x.cuda(), gx.cuda(), ga.cuda(), lam.cuda(), h2, go.cuda())
+    for a, b in zip(grads, (xs[0].grad, xs[1].grad, xs[2].grad, lam_d.grad)):
+        assert torch.equal(a, b)
