@@ -672,6 +672,18 @@ def fused_cross_entropy(lm_head_weight, act, labels):
     return linear_ce(lm_head_weight, act, labels)[0]
 
 
+class CrossEntropyLoopedFused:
+    """The reference's autograd class by name (hawk/fused_cross_entropy.py:11-73): `.apply(weight, act, labels)`
+    is fused_cross_entropy (one pass over all rows here, no chunk loop)."""
+    apply = staticmethod(fused_cross_entropy)
+
+
+class DiagonalRecurrence:
+    """The reference's autograd class by name (hawk/scan_fused.py:426-442): `.apply(x, x_rg_lru, a_rg_lru, a_param)`
+    is fused_linear_scan (:445)."""
+    apply = staticmethod(fused_linear_scan)
+
+
 # ---------------------------------------------------------------------------------------------
 # glue around the GEMMs: gelu(a) * b and RMSNorm, one pass each
 # ---------------------------------------------------------------------------------------------

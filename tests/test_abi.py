@@ -188,3 +188,11 @@ def test_time_split_policy_and_validation_need_no_gpu():
     assert lib.hawk_scan_fwd_split(*args(65, big, T=65 * 64)) < 0   # more pieces than supported
     assert lib.hawk_scan_fwd_split(*args(4, 16)) < 0                # workspace too small
     assert lib.hawk_scan_fwd_split(p, p, p, p, None, None, p, 0, 0, p, None, 4, p, big, 1, 1024, 64, 1, None) < 0  # y without out
+
+
+def test_reference_class_names_resolve_to_the_operators():
+    """hawk/scan_fused.py:426-445 and hawk/fused_cross_entropy.py:11-79 expose their operators as
+    `Class.apply`; the same spellings work here."""
+    from hawk_b200 import ops
+    assert ops.DiagonalRecurrence.apply is ops.fused_linear_scan
+    assert ops.CrossEntropyLoopedFused.apply is ops.fused_cross_entropy
